@@ -199,13 +199,21 @@ class CacheManager:
 
 def build_groups(needs: list, page_size: int) -> list[CacheGroup]:
     """Sorts the schedule's runs into groups. ``needs[i]`` is the ``CacheNeed`` of run i, or None when the run
-    keeps nothing or reads another run's cache. Paged runs with the same (window, kv_heads, head_dim, planes) share a
+    keeps nothing or reads another run's cache; a tuple of them for a run whose mixer is several side by side (branch j's
+    cache is then known as (i, j)). ``needs`` may also be a dict from any such key to its need (the embedding's state goes
+    under a key of its own). Paged runs with the same (window, kv_heads, head_dim, planes) share a
     group; every state run with the same shape and dtype shares one. A group of fixed-size state always exists,
     with no runs and a zero-sized state when the model has none, so that slots are handed out and returned on
     every path."""
     paged: dict[tuple, list[int]] = {}
     state: dict[tuple, list[int]] = {}
-    for i, need in enumerate(needs):
+    flat = []
+    for i, need in (needs.items() if isinstance(needs, dict) else enumerate(needs)):
+        if isinstance(need, (tuple, list)):
+            flat += [((i, j), sub) for j, sub in enumerate(need)]
+        else:
+            flat.append((i, need))
+    for i, need in flat:
         if need is None:
             continue
         if need.kind == "paged":

@@ -15,7 +15,8 @@ from dataclasses import dataclass, field
 @dataclass(frozen=True)
 class NormSpec:
     """``rms_norm``: x / sqrt(mean(x^2) + eps) * w. ``layer_norm``: (x - mean) / sqrt(var + eps) * w + b, var the mean squared
-    deviation; it reads a 32-bit stream and writes the activation dtype. ``weight_offset``: what is added to the stored
+    deviation; it reads a 32-bit stream and writes the activation dtype. ``rms_norm_wide``: the first over a 32-bit stream,
+    written in the activation dtype. ``weight_offset``: what is added to the stored
     weight before it multiplies (1.0 for weights stored around zero)."""
     size: int
     eps: float
@@ -82,7 +83,9 @@ class SinkAttentionSpec(MixerSpec):
     """Grouped-query causal attention whose values have a size of their own (``v_dim``) and whose softmax may have a sink:
     with ``sink`` the denominator is 1 + sum exp(s_j), a key of score 0 that has no value. Queries and keys are rotated
     (``position``) and then, with ``unit_norm_eps`` set, divided by their root mean square over ``head_dim`` (eps inside the
-    root, no weight). Every earlier key is seen. The cache keeps one entry [key | value] a token and key/value head."""
+    root, no weight). ``window`` counts the keys a query sees, its own included (None: every earlier key). With ``softcap``
+    c > 0 a score s (already scaled) becomes c tanh(s / c). ``bias``: the q, k and v projections add a stored vector. The
+    cache keeps one entry [key | value] a token and key/value head, or keys and values in two planes when their sizes agree."""
     kind: str = "sink_attention"
     hidden: int = 0
     num_heads: int = 0
@@ -93,6 +96,9 @@ class SinkAttentionSpec(MixerSpec):
     sink: bool = True
     unit_norm_eps: float | None = None
     position: PositionSpec | None = None
+    window: int | None = None
+    softcap: float = 0.0
+    bias: bool = False
 
 
 @dataclass(frozen=True)
@@ -125,6 +131,50 @@ class Mamba2Spec(MixerSpec):
     groups: int = 1
     conv_taps: int = 4
     norm_groups: int = 1
+    eps: float = 1e-6
+
+
+@dataclass(frozen=True)
+class GatedRecurrenceSpec(MixerSpec):
+    """A gated linear recurrence a channel (the real-gated linear recurrent unit) between two branches of ``width`` channels:
+    y = gelu_tanh(W_y h + b_y); u = conv(W_x h + b_x), a causal convolution of ``conv_taps`` taps a channel with a bias and no
+    activation. u is cut into ``blocks`` equal parts; in each, r = sigmoid(R_b u_b + b) and i = sigmoid(I_b u_b + b) with square
+    matrices; a = exp(-``rate`` r softplus(lam)); S <- a S + sqrt(1 - a^2) i u from S = 0; the output is W_o (S y). S and the
+    convolution's last ``conv_taps`` - 1 inputs are kept per request in 32-bit."""
+    kind: str = "gated_recurrence"
+    hidden: int = 0
+    width: int = 0
+    blocks: int = 1
+    conv_taps: int = 4
+    rate: float = 8.0
+
+
+@dataclass(frozen=True)
+class MatrixMemorySpec(MixerSpec):
+    """A matrix memory a head with exponential gates (the mLSTM cell). q = W_q h / sqrt(head_dim), k = W_k h, v = W_v h; per
+    head the logarithms of an input gate i = c tanh((W_i h + b) / c) and of a forget gate f = logsigmoid(c tanh((W_f h + b) / c)),
+    c = ``gate_cap``; with a running maximum m (from 0): m' = max(f + m, i), S <- exp(f + m - m') S + exp(i - m') k v^T, n likewise
+    with k alone, o = S^T q / (max(|n . q|, exp(-m')) + ``floor``). Each head's o is divided by its root mean square (``eps``),
+    the heads side by side are multiplied by a weight and by sigmoid(W_g h), then projected out. S, n and m are kept per
+    request in 32-bit."""
+    kind: str = "matrix_memory"
+    hidden: int = 0
+    num_heads: int = 0
+    head_dim: int = 0
+    v_dim: int = 0
+    gate_cap: float = 0.0
+    eps: float = 1e-6
+    floor: float = 1e-6
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec(MixerSpec):
+    """Several mixers side by side that read the same input; the result is the mean of their outputs, each first divided by
+    its root mean square over the model width (``eps``) and multiplied by a weight of its own. Every branch keeps the cache
+    or state its own kind asks for."""
+    kind: str = "parallel"
+    hidden: int = 0
+    branches: tuple = ()
     eps: float = 1e-6
 
 
@@ -207,6 +257,30 @@ class CappedHeadSpec(HeadSpec):
 
 
 @dataclass(frozen=True)
+class PairHashedEmbeddingSpec(EmbeddingSpec):
+    """h0[t] = table[id_t] + pairs[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets] as a 32-bit stream; a request's first
+    token takes row ``buckets`` of ``pairs`` (the row after the buckets). The previous token is kept per request."""
+    kind: str = "pair_hashed_table"
+    buckets: int = 0
+    mul_prev: int = 0
+    mul_cur: int = 0
+
+
+@dataclass(frozen=True)
+class TokenInputSpec:
+    """What a layer adds to the stream at its end from the token itself: e = ``dim`` numbers of a second embedding table (the
+    columns from ``column`` on of a table ``columns`` wide), g = gelu_tanh(W_gate x) * e, y = W_proj g, and the stream gains
+    y / sqrt(mean(y^2) + eps) * w."""
+    kind: str = "gated_token_input"
+    hidden: int = 0
+    vocab: int = 0
+    dim: int = 0
+    column: int = 0
+    columns: int = 0
+    eps: float = 1e-6
+
+
+@dataclass(frozen=True)
 class ConnectionSpec:
     """How a sublayer reads the residual and writes back to it. ``hyper_connection``: the residual is ``streams`` copies
     x_1 .. x_S in 32-bit, all equal to the embedding at the start; the sublayer reads u = sum_s in[s] x_s and its output y
@@ -229,15 +303,18 @@ class BlockSpec:
     post_mixer_norm: NormSpec | None
     kind: str = "pre_norm"
     connection: ConnectionSpec | None = None
+    token_input: TokenInputSpec | None = None     # ``pre_norm_wide`` only: added after the last sublayer
 
 
 @dataclass(frozen=True)
 class RunEntry:
     """One run of a block. ``block`` indexes ``ModelSpec.blocks`` (the same block may run twice: it then has
     one set of weights and two caches). ``reads_cache_of`` is None when the run keeps a cache of its own, or
-    the index of an earlier run whose cache it reads without writing."""
+    the index of an earlier run whose cache it reads without writing. ``adds_embedding``: the embedding's output is added to
+    the residual stream once more right before the run (a model that runs a range of blocks several times)."""
     block: int
     reads_cache_of: int | None = None
+    adds_embedding: bool = False
 
 
 @dataclass(frozen=True)

@@ -173,7 +173,7 @@ class StepExecutor:
         self.model = model
         self.rt = model.rt
         self.page_size = page_size
-        self.groups = build_groups(model.cache_needs, page_size)
+        self.groups = build_groups(model.cache_keys() if hasattr(model, "cache_keys") else model.cache_needs, page_size)
         elem = torch.empty((), dtype=self.rt.dtype).element_size()
         if num_pages is None and max_tokens is not None:
             num_pages = -(-max_tokens // page_size)
@@ -194,7 +194,8 @@ class StepExecutor:
         self.mixers = [b.mixer for b in model.blocks]
         state_runs = {r for g in self.groups if g.kind == "state" for r in g.runs}
         self.use_graphs = (use_graphs and self.rt.device.type == "cuda"
-                           and all(getattr(model.blocks[model.spec.schedule[r].block].mixer, "state_capturable", False) for r in state_runs)
+                           and all(getattr(model.cache_owner(r) if hasattr(model, "cache_owner") else model.blocks[model.spec.schedule[r].block].mixer,
+                                           "state_capturable", False) for r in state_runs)
                            and all(getattr(p, "capturable", True) for p in model.parts()))
         self._graphs: dict = {}
         self._graph_pool = None

@@ -44,6 +44,7 @@ class Model:
         self.head = HEADS.build(spec.head, runtime)
         # what each run keeps between steps (None: nothing, or another run's cache)
         self.cache_needs = []
+        self.embedding_need = self.embedding.cache_need()
         for n, e in enumerate(spec.schedule):
             need = self.blocks[e.block].mixer.cache_need()
             if e.reads_cache_of is not None:
@@ -53,6 +54,28 @@ class Model:
                                      f"({owner} against {need})")
                 need = None
             self.cache_needs.append(need)
+
+    EMBEDDING_CACHE = "embedding"     # the key of the embedding's state among the cache groups' runs
+
+    def cache_keys(self) -> dict:
+        """What the cache manager sorts into groups: run index -> need (a tuple for a mixer of several side by side), and
+        the embedding's state under a key of its own."""
+        needs = dict(enumerate(self.cache_needs))
+        if self.embedding_need is not None:
+            needs[self.EMBEDDING_CACHE] = self.embedding_need
+        return needs
+
+    def cache_owner(self, key):
+        """The part whose state lives under ``key`` of a cache group's runs."""
+        if key == self.EMBEDDING_CACHE:
+            return self.embedding
+        return self.blocks[self.spec.schedule[key[0] if isinstance(key, tuple) else key].block].mixer
+
+    def cache_view(self, storage, run: int):
+        need = self.cache_needs[run]
+        if isinstance(need, tuple):
+            return tuple(storage.view((run, j)) for j in range(len(need)))
+        return storage.view(run)
 
     # ------------------------------------------------------------------ weights
     def _place(self, t: torch.Tensor, decl: ParamDecl) -> torch.Tensor:
@@ -112,11 +135,17 @@ class Model:
     def forward(self, batch, storage) -> torch.Tensor:
         """Logits [selected, vocab] in float32 for ``batch.selected`` (an empty tensor when nothing is wanted)."""
         k = self.rt.kernels
-        h = self.embedding(batch.ids, batch)
+        if self.embedding_need is not None:
+            h = self.embedding(batch.ids, batch, storage.view(self.EMBEDDING_CACHE))
+        else:
+            h = self.embedding(batch.ids, batch)
+        # a run that adds the embedding's output again reads a copy: the first block sums into the stream it was handed
+        embedded = h.clone() if any(e.adds_embedding for e in self.spec.schedule) else None
         residual = None
         for n, e in enumerate(self.spec.schedule):
             owner = n if e.reads_cache_of is None else e.reads_cache_of
-            h, residual = self.blocks[e.block](h, residual, batch, storage.view(owner), write_cache=e.reads_cache_of is None)
+            more = {"stream_input": embedded} if e.adds_embedding else {}
+            h, residual = self.blocks[e.block](h, residual, batch, self.cache_view(storage, owner), write_cache=e.reads_cache_of is None, **more)
         if batch.num_selected == 0:
             return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=self.rt.device)
         close = getattr(self.blocks[self.spec.schedule[-1].block], "close", None)

@@ -32,6 +32,9 @@ class ParamDecl:
     # how the random-weights mode draws the parameter when the role's default (matrices N(0, std), vectors 1 + N(0, norm_std))
     # does not suit it: ("normal", mean, std), ("uniform", low, high) or ("eye_normal", scale, std): scale * identity + N(0, std)
     init: tuple | None = None
+    # (start, stop, total): the parameter is the columns [start, stop) of a checkpoint tensor ``total`` columns wide (several
+    # parts may each take their own columns of one stored table)
+    columns: tuple | None = None
 
 
 @dataclass(frozen=True)
@@ -101,7 +104,9 @@ class Mixer(Part):
     # the rows is then right as it is).
     state_capturable = False
 
-    def cache_need(self) -> CacheNeed | None:
+    def cache_need(self) -> CacheNeed | tuple | None:
+        """What a run of the mixer keeps between steps. A mixer made of several (``parallel``) returns a tuple with one entry a
+        branch (a ``CacheNeed`` or None); its call then gets a tuple of cache views in the same order."""
         return None
 
     # ---- per-step work lists (optional). A mixer whose kernels want lists derived on the host from the step's rows
@@ -154,12 +159,26 @@ class Embedding(Part):
     def tied_weight(self) -> torch.Tensor | None:
         return None
 
+    def cache_need(self) -> CacheNeed | None:
+        """State the embedding keeps per request between steps (a previous token, say), or None. An embedding with a need is
+        called with a third argument, its view of that state; it must read the step's device tables only."""
+        return None
+
 
 class Head(Part):
     """The final hidden states of the wanted rows to float32 logits [rows, vocab]. Declares its parameters under the scope
     "lm_head"; with tied embeddings it declares none and is loaded with {"weight": the embedding's ``tied_weight``}."""
 
     def __call__(self, final: torch.Tensor, batch) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class TokenInput(Part):
+    """What a block adds to the residual stream from the token ids themselves (``TokenInputSpec``). Declares its parameters
+    under the scope "blocks.<i>.token_input". ``__call__(x, ids)``: x is the stream's value in the activation dtype, the result
+    the addend."""
+
+    def __call__(self, x: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
 
@@ -205,6 +224,7 @@ BLOCKS = _Registry("block arrangement")
 EMBEDDINGS = _Registry("embedding")
 HEADS = _Registry("head")
 CONNECTIONS = _Registry("residual connection")
+TOKEN_INPUTS = _Registry("token input")
 
 
 def register_norm(kind, cls):
@@ -237,3 +257,7 @@ def register_head(kind, cls):
 
 def register_connection(kind, cls):
     CONNECTIONS.register(kind, cls)
+
+
+def register_token_input(kind, cls):
+    TOKEN_INPUTS.register(kind, cls)

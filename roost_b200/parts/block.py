@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 
 from ..config.spec import BlockSpec
-from .base import CONNECTIONS, FEED_FORWARDS, MIXERS, NORMS, Block, Runtime, register_block
+from .base import CONNECTIONS, FEED_FORWARDS, MIXERS, NORMS, TOKEN_INPUTS, Block, Runtime, register_block
 
 
 class PreNormBlock(Block):
@@ -44,7 +44,9 @@ class PreNormBlock(Block):
 class PreNormWideBlock(Block):
     """The same arrangement over a stream that is kept and summed in 32-bit whatever the activation dtype is: the
     embedding hands over a float32 stream, every norm reads it (adding the branch output before it first, in 32-bit)
-    and writes the activation dtype. The feed-forward and its norm may be absent."""
+    and writes the activation dtype. The feed-forward and its norm may be absent. With ``token_input`` the layer ends with one
+    more sum: what that part makes of the stream's value and the token ids. A run may be handed ``stream_input``, a 32-bit
+    tensor that is added to the stream right before the run's first norm (the embedding's output added again)."""
 
     def __init__(self, spec: BlockSpec, runtime: Runtime):
         self.spec = spec
@@ -57,11 +59,18 @@ class PreNormWideBlock(Block):
                 raise ValueError("pre_norm_wide: a feed-forward needs the norm before it")
             self.post_mixer_norm = NORMS.build(spec.post_mixer_norm, runtime)
             self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, runtime)
+        self.token_input = None
+        if spec.token_input is not None:
+            if not hasattr(self.input_norm, "add_only"):
+                raise ValueError(f"pre_norm_wide: a token input needs a norm that hands the stream on without norming it; '{spec.input_norm.kind}' does not")
+            self.token_input = TOKEN_INPUTS.build(spec.token_input, runtime)
 
     def sub_parts(self):
         parts = {"input_norm": self.input_norm, "mixer": self.mixer}
         if self.feed_forward is not None:
             parts.update({"post_mixer_norm": self.post_mixer_norm, "feed_forward": self.feed_forward})
+        if self.token_input is not None:
+            parts["token_input"] = self.token_input
         return parts
 
     @classmethod
@@ -69,21 +78,31 @@ class PreNormWideBlock(Block):
         subs = {"input_norm": (NORMS, spec.input_norm), "mixer": (MIXERS, spec.mixer)}
         if spec.feed_forward is not None:
             subs.update({"post_mixer_norm": (NORMS, spec.post_mixer_norm), "feed_forward": (FEED_FORWARDS, spec.feed_forward)})
+        if spec.token_input is not None:
+            subs["token_input"] = (TOKEN_INPUTS, spec.token_input)
         return subs
 
-    def __call__(self, h, residual, batch, cache, write_cache: bool = True):
+    def __call__(self, h, residual, batch, cache, write_cache: bool = True, stream_input=None):
         if residual is None:
             if h.dtype != torch.float32:
                 raise ValueError("pre_norm_wide: the embedding must hand over a float32 stream")
+            if stream_input is not None:
+                raise ValueError("pre_norm_wide: the first run cannot add to a stream that does not exist yet")
             residual = h
             x = self.input_norm(h)
+        elif stream_input is not None:
+            x, residual = self.input_norm.add_norm(h, residual, extra=stream_input)
         else:
             x, residual = self.input_norm.add_norm(h, residual)
         a = self.mixer(x, batch, cache, write_cache)
-        if self.feed_forward is None:
-            return a, residual
-        y, residual = self.post_mixer_norm.add_norm(a, residual)
-        return self.feed_forward(y, batch), residual
+        if self.feed_forward is not None:
+            y, residual = self.post_mixer_norm.add_norm(a, residual)
+            a = self.feed_forward(y, batch)
+        if self.token_input is not None:
+            # the stream's own value (the last branch output added, not normed) is what the token input reads
+            x, residual = self.input_norm.add_only(a, residual)
+            a = self.token_input(x, batch.ids)
+        return a, residual
 
 
 class StreamState:

@@ -64,5 +64,38 @@ class LayerNorm(Norm):
         return out, residual
 
 
+class WideRmsNorm(Norm):
+    """x / sqrt(mean(x^2) + eps) * w over a 32-bit stream; the output has the activation dtype. ``add_norm`` adds a branch
+    output (activation dtype) to the stream in 32-bit first, and with ``extra`` a second 32-bit addend (the embedding's output
+    added again): the stream is never rounded. ``add_only`` makes the sums and hands the stream's value on in the activation
+    dtype without a norm (for a part that reads the stream itself)."""
+
+    def __init__(self, spec: NormSpec, runtime: Runtime):
+        if spec.size <= 0 or spec.eps <= 0:
+            raise ValueError(f"rms_norm_wide: size {spec.size} and eps {spec.eps} must be positive")
+        self.spec = spec
+        self.rt = runtime
+        self.weight: torch.Tensor | None = None
+
+    @classmethod
+    def parameters(cls, spec: NormSpec):
+        return {"weight": ParamDecl(shape=(spec.size,), role="vector")}
+
+    def load(self, params):
+        self.weight = (params["weight"].float() + float(self.spec.weight_offset)).contiguous()
+
+    def __call__(self, x: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
+        return self.rt.kernels.wide_rms_norm(x, self.weight, self.spec.eps, self.rt.dtype, None, None, rows)
+
+    def add_norm(self, x: torch.Tensor, residual: torch.Tensor, rows: torch.Tensor | None = None, extra: torch.Tensor | None = None):
+        """Returns (norm(residual + x [+ extra]), the sum); without ``rows`` the sum replaces ``residual`` in place."""
+        return self.rt.kernels.wide_rms_norm(residual, self.weight, self.spec.eps, self.rt.dtype, x, extra, rows), residual
+
+    def add_only(self, x: torch.Tensor, residual: torch.Tensor):
+        """Returns (residual + x in the activation dtype, the sum, which replaces ``residual`` in place)."""
+        return self.rt.kernels.wide_rms_norm(residual, None, self.spec.eps, self.rt.dtype, x, None, None), residual
+
+
+register_norm("rms_norm_wide", WideRmsNorm)
 register_norm("rms_norm", RmsNorm)
 register_norm("layer_norm", LayerNorm)

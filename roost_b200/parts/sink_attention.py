@@ -1,10 +1,12 @@
 """Grouped-query causal attention with a sink in the softmax, unit-norm queries and keys, and values of their own size.
 
-Per step: one fused q/k/v projection (rows [q heads | k heads | v heads]); one kernel that rotates the query and key heads
-(interleaved pairs, angles formed in double precision), divides each by its root mean square over the head (no weight), writes
-the query back in place and the key and value into the step's page slots; attention of the step's queries over the pages with
-p_j = exp(s_j) / (1 + sum exp(s_j)) (with ``sink``; the plain softmax without), scores and weights in 32-bit; the output
-projection over the concatenated heads.
+Per step: one fused q/k/v projection (rows [q heads | k heads | v heads], with a bias where the spec says so); one kernel that
+rotates the query and key heads (interleaved pairs or split halves, as the position encoding says; angles formed in double
+precision), divides each by its root mean square over the head (no weight), writes the query back in place and the key and
+value into the step's page slots; attention of the step's queries over the pages with p_j = exp(s_j) / (1 + sum exp(s_j)) (with
+``sink``; the plain softmax without), scores and weights in 32-bit, over every earlier key or the last ``window`` (the cache
+group then gives back the pages the window has passed), a score s becoming c tanh(s / c) with ``softcap`` c; the output projection
+over the concatenated heads.
 
 The cache is a paged group. When keys and values have the same size it has two planes (keys, values), the layout of the
 framework's tensor-core attention kernels, which then serve the bfloat16 steps with the sink added at their end; otherwise it
@@ -45,26 +47,34 @@ class SinkAttention(Mixer):
         self.out = Linear(runtime, s.hidden, s.num_heads * s.v_dim)
         self.position = POSITIONS.build(s.position, runtime) if s.position is not None else None
         if self.position is not None and self.position.rotation()[1]:
-            if getattr(self.position, "pairing", None) != "interleaved":
-                raise ValueError(f"sink_attention: the kernel rotates interleaved pairs; position encoding '{s.position.kind}' pairs otherwise")
+            if getattr(self.position, "pairing", None) not in ("interleaved", "halves"):
+                raise ValueError(f"sink_attention: the kernel rotates interleaved pairs or split halves; position encoding '{s.position.kind}' pairs otherwise")
             if self.position.rotation()[1] > s.head_dim:
                 raise ValueError("sink_attention: the rotation is wider than a head")
+        if s.window is not None and s.window <= 0:
+            raise ValueError(f"sink_attention: a window of {s.window} keys must be positive")
+        if s.softcap < 0:
+            raise ValueError(f"sink_attention: the scores' cap {s.softcap} cannot be negative")
+        self.halves = self.position is not None and getattr(self.position, "pairing", None) == "halves"
         self.two_planes = s.head_dim == s.v_dim
 
     @classmethod
     def parameters(cls, spec: SinkAttentionSpec):
         Q, K, V = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim, spec.num_kv_heads * spec.v_dim
-        return {"qkv": ParamDecl(shape=(Q + K + V, spec.hidden), row_splits=(Q, K, V)), "out": ParamDecl(shape=(spec.hidden, spec.num_heads * spec.v_dim))}
+        decls = {"qkv": ParamDecl(shape=(Q + K + V, spec.hidden), row_splits=(Q, K, V)), "out": ParamDecl(shape=(spec.hidden, spec.num_heads * spec.v_dim))}
+        if spec.bias:
+            decls["qkv_bias"] = ParamDecl(shape=(Q + K + V,), row_splits=(Q, K, V), role="vector", init=("normal", 0.0, 0.1))
+        return decls
 
     def load(self, params):
-        self.qkv.load(params["qkv"])
+        self.qkv.load(params["qkv"], params["qkv_bias"] if self.spec.bias else None)
         self.out.load(params["out"])
 
     def cache_need(self) -> CacheNeed:
         s = self.spec
         if self.two_planes:
-            return CacheNeed(kind="paged", kv_heads=s.num_kv_heads, head_dim=s.head_dim, planes=2)
-        return CacheNeed(kind="paged", kv_heads=s.num_kv_heads, head_dim=s.head_dim + s.v_dim, planes=1)
+            return CacheNeed(kind="paged", kv_heads=s.num_kv_heads, head_dim=s.head_dim, planes=2, window=s.window)
+        return CacheNeed(kind="paged", kv_heads=s.num_kv_heads, head_dim=s.head_dim + s.v_dim, planes=1, window=s.window)
 
     def __call__(self, x, batch, cache, write_cache: bool = True):
         s, k = self.spec, self.rt.kernels
@@ -73,16 +83,19 @@ class SinkAttention(Mixer):
         tables = batch.groups[cache.group]
         inv_freq, rotary_dim = self.position.rotation() if self.position is not None else (None, 0)
         qkv = self.qkv(x)
-        tensor_cores = (self.two_planes and qkv.dtype == torch.bfloat16 and getattr(k, "attention_mma_sink", False)
+        # the tensor-core kernels rotate nothing themselves and know no cap on the scores: a capped model runs the 32-bit kernel
+        tensor_cores = (self.two_planes and qkv.dtype == torch.bfloat16 and not s.softcap and getattr(k, "attention_mma_sink", False)
                         and getattr(k, "attention_mma_supported", lambda d: False)(s.head_dim))
         q = torch.empty((qkv.shape[0], s.num_heads, s.head_dim), dtype=qkv.dtype, device=qkv.device) if tensor_cores else None
         k.sink_attention_prepare(qkv, cache.k_pool, cache.v_pool, inv_freq, rotary_dim, batch.positions, tables.slot_mapping, s.num_heads,
-                                 s.num_kv_heads, s.head_dim, s.v_dim, s.unit_norm_eps, cache.page_size, **({"q_out": q} if tensor_cores else {}))
+                                 s.num_kv_heads, s.head_dim, s.v_dim, s.unit_norm_eps, cache.page_size, **({"q_out": q} if tensor_cores else {}),
+                                 **({"halves": True} if self.halves else {}))
         if tensor_cores:
             o = self._attend_tensor_cores(q, batch, cache, tables)
         else:
             o = k.sink_attention(qkv, cache.k_pool, cache.v_pool, batch.positions, batch.token_row, tables.kv_indptr, tables.kv_indices,
-                                 s.num_heads, s.num_kv_heads, s.head_dim, s.v_dim, s.scale, s.sink, kv_cap=batch.kv_cap)
+                                 s.num_heads, s.num_kv_heads, s.head_dim, s.v_dim, s.scale, s.sink, kv_cap=batch.kv_cap,
+                                 **({"window": s.window} if s.window is not None else {}), **({"softcap": s.softcap} if s.softcap else {}))
         return self.out(o)
 
     # ---- bfloat16 with keys and values of one size: the framework's tensor-core kernels, with the sink
@@ -92,9 +105,9 @@ class SinkAttention(Mixer):
         tile_rows = k.attention_prefill_tile_rows(s.num_heads, cache.k_pool, cache.v_pool, batch.num_tokens * group, tensor_memory=False)
         split_for = getattr(k, "decode_split_for", None)
         chunk, cluster = split_for(batch.num_rows, batch.kv_cap, cache.k_pool, cache.v_pool) if split_for and batch.kv_cap else (k.decode_chunk, 0)
-        plan = batch.step_work(self, ("sink_attention", group, None, chunk, tile_rows, cluster))
+        plan = batch.step_work(self, ("sink_attention", group, s.window, chunk, tile_rows, cluster))
         return k.attention_mma(q, cache.k_pool, cache.v_pool, batch.q_indptr, batch.kv_lens, tables.kv_indptr, tables.kv_indices, plan,
-                               s.scale, None, sink=s.sink, wide_weights=True)
+                               s.scale, s.window, sink=s.sink, wide_weights=True)
 
     def step_class(self, row_counts):
         return ("short_rows", any(n <= SHORT_ROW_TOKENS for n in row_counts))

@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from ..config.spec import EmbeddingSpec, HeadSpec
-from .base import Embedding, Head, ParamDecl, Runtime, register_embedding, register_head
+from .base import CacheNeed, Embedding, Head, ParamDecl, Runtime, register_embedding, register_head
 from .linear import Linear
 
 
@@ -78,6 +78,41 @@ class CappedLinearHead(LinearHead):
         return self.rt.kernels.softcap_(self.linear(final, out_dtype=torch.float32), float(self.spec.cap))
 
 
+class PairHashedEmbedding(TableEmbedding):
+    """h0[t, :] = table[id_t, :] + pairs[row_t, :] as a float32 stream, row_t = (id_(t-1) * mul_prev + id_t * mul_cur) mod
+    buckets, and the row after the buckets for a request's first token. The token before a step's first token of a request
+    is kept on the device, one int32 a request (a state group of the cache manager): the kernel reads it through the step's
+    slot table and a second kernel stores the row's last token, so steps replay from graphs and a step started ahead of the
+    host finds its predecessor's token where it left it."""
+    state_capturable = True
+
+    def __init__(self, spec, runtime: Runtime):
+        super().__init__(spec, runtime)
+        if spec.buckets <= 0 or spec.mul_prev < 0 or spec.mul_cur < 0:
+            raise ValueError("pair_hashed_table: buckets must be positive and the multipliers not negative")
+        self.pairs: torch.Tensor | None = None
+
+    @classmethod
+    def parameters(cls, spec):
+        return {"table": ParamDecl(shape=(spec.vocab, spec.hidden)), "pairs": ParamDecl(shape=(spec.buckets + 1, spec.hidden))}
+
+    def load(self, params):
+        super().load(params)
+        self.pairs = params["pairs"].to(self.rt.dtype).contiguous()
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(kind="state", state_shape=(1,), state_dtype=torch.int32)
+
+    def __call__(self, ids, batch, cache=None):
+        s, k = self.spec, self.rt.kernels
+        slots = batch.groups[cache.group].state_slots
+        out = k.pair_embedding(self.table, self.pairs, ids, batch.positions, batch.token_row, batch.q_indptr, slots, cache.state,
+                               s.buckets, s.mul_prev, s.mul_cur)
+        k.last_token_store(ids, batch.q_indptr, slots, cache.state)
+        return out
+
+
+register_embedding("pair_hashed_table", PairHashedEmbedding)
 register_embedding("table", TableEmbedding)
 register_embedding("scaled_table", ScaledTableEmbedding)
 register_head("capped_linear", CappedLinearHead)

@@ -57,7 +57,8 @@ def resolve(reader: ConfigReader) -> Architecture:
 
 
 def _register_builtin() -> None:
-    from .config import lafanex, qwen3, vamatar
+    from .config import lafanex, nomivik, qwen3, vamatar
+    register_architecture(nomivik.ARCHITECTURE, read_config=nomivik.NomivikConfig.from_reader, to_spec=lambda cfg, tied=None: cfg.to_spec(tied))
     register_architecture(lafanex.ARCHITECTURE, read_config=lafanex.LafanexConfig.from_reader, to_spec=lambda cfg, tied=None: cfg.to_spec(tied))
     register_architecture(vamatar.ARCHITECTURE, read_config=vamatar.VamatarConfig.from_reader, to_spec=lambda cfg, tied=None: cfg.to_spec(tied))
     register_architecture(qwen3.ARCHITECTURE, model_types=(qwen3.MODEL_TYPE,), read_config=qwen3.Qwen3Config.from_reader,

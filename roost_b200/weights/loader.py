@@ -75,7 +75,11 @@ def expected_tensors(decls: dict, names: dict) -> dict[str, tuple]:
                 srcs = names[scope][local]
             except KeyError:
                 raise WeightError(f"the architecture names no checkpoint tensor for parameter '{local}' of '{scope}'") from None
-            if len(srcs) == 1:
+            if decl.columns is not None:      # the parameter is a range of columns of one stored tensor
+                if len(srcs) != 1 or len(decl.shape) != 2 or decl.columns[1] - decl.columns[0] != decl.shape[1]:
+                    raise WeightError(f"parameter '{local}' of '{scope}' takes columns {decl.columns} but is declared {decl.shape} over {len(srcs)} tensors")
+                out[srcs[0]] = (decl.shape[0], decl.columns[2])
+            elif len(srcs) == 1:
                 out[srcs[0]] = tuple(decl.shape)
             else:
                 if decl.row_splits is None or len(decl.row_splits) != len(srcs):
@@ -143,8 +147,10 @@ def load_checkpoint(model_dir, decls: dict, names: dict, allow_unexpected=()) ->
         out: dict[str, dict[str, torch.Tensor]] = {}
         for scope, params in decls.items():
             out[scope] = {}
-            for local in params:
+            for local, decl in params.items():
                 parts = [_stored(where[n].tensor(n)) for n in names[scope][local]]
+                if decl.columns is not None:
+                    parts = [parts[0][:, decl.columns[0] : decl.columns[1]].contiguous()]
                 out[scope][local] = parts[0] if len(parts) == 1 else torch.cat(parts, dim=0)
         return out
     finally:

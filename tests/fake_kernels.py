@@ -159,7 +159,7 @@ class FakeKernels:
         return out
 
     # ---- mamba-2
-    def mamba2_conv(self, u, col, channels, w, b, state, conv_off, token_row, q_indptr, slots):
+    def mamba2_conv(self, u, col, channels, w, b, state, conv_off, token_row, q_indptr, slots, activation="silu"):
         T, taps = u.shape[0], w.shape[1]
         out = torch.zeros(T, channels, dtype=torch.float32)
         for t in range(T):
@@ -174,7 +174,7 @@ class FakeKernels:
                     j = i - start + (taps - 1)
                     v = state[slot, conv_off + j * channels : conv_off + (j + 1) * channels]
                 acc = acc + w[:, k] * v
-            out[t] = acc / (1 + torch.exp(-acc))
+            out[t] = acc / (1 + torch.exp(-acc)) if activation == "silu" else acc
         return out.to(u.dtype)
 
     def mamba2_conv_state(self, u, col, channels, taps, state, conv_off, q_indptr, slots):
@@ -299,7 +299,8 @@ class FakeKernels:
         return (u * torch.rsqrt((u * u).mean(-1, keepdim=True) + eps) * norm_w.float()).to(out_dtype)
 
     # ---- attention with a sink
-    def sink_attention_prepare(self, qkv, k_pool, v_pool, inv_freq, rotary_dim, positions, slot_mapping, heads, kv_heads, dim, vdim, eps, page_size):
+    def sink_attention_prepare(self, qkv, k_pool, v_pool, inv_freq, rotary_dim, positions, slot_mapping, heads, kv_heads, dim, vdim, eps, page_size,
+                               halves=False):
         T = qkv.shape[0]
         Q, K = heads * dim, kv_heads * dim
 
@@ -307,9 +308,10 @@ class FakeKernels:
             if rotary_dim:
                 ang = positions.double()[:, None] * inv_freq[None, :]
                 c, s = torch.cos(ang)[:, None, :].float(), torch.sin(ang)[:, None, :].float()
-                u, v = x[..., 0:rotary_dim:2].clone(), x[..., 1:rotary_dim:2].clone()
-                x[..., 0:rotary_dim:2] = u * c - v * s
-                x[..., 1:rotary_dim:2] = v * c + u * s
+                first, second = (slice(0, rotary_dim // 2), slice(rotary_dim // 2, rotary_dim)) if halves else (slice(0, rotary_dim, 2), slice(1, rotary_dim, 2))
+                u, v = x[..., first].clone(), x[..., second].clone()
+                x[..., first] = u * c - v * s
+                x[..., second] = v * c + u * s
             if eps is not None:
                 x = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps)
             return x
@@ -329,7 +331,8 @@ class FakeKernels:
                 k_pool[page, :, off, :] = k[t]
                 v_pool[page, :, off, :] = v[t]
 
-    def sink_attention(self, qkv, k_pool, v_pool, positions, token_row, kv_indptr, kv_indices, heads, kv_heads, dim, vdim, scale, sink, kv_cap=0):
+    def sink_attention(self, qkv, k_pool, v_pool, positions, token_row, kv_indptr, kv_indices, heads, kv_heads, dim, vdim, scale, sink, kv_cap=0,
+                       window=None, softcap=0.0):
         T = qkv.shape[0]
         page_size = k_pool.shape[2]
         out = torch.zeros(T, heads * vdim, dtype=qkv.dtype)
@@ -340,17 +343,125 @@ class FakeKernels:
                 continue
             r = int(token_row[t])
             pages = kv_indices[int(kv_indptr[r]) : int(kv_indptr[r + 1])].long()
-            entries = k_pool[pages].permute(1, 0, 2, 3).reshape(kv_heads, -1, k_pool.shape[3])[:, : pos + 1].float()
+            lo = max(0, pos - window + 1) if window else 0
+            first_page = lo // page_size            # pages before it may have been given back (entry -1): never touched
+            pages, lo = pages[first_page:], lo - first_page * page_size
+            hi = pos + 1 - first_page * page_size
+            entries = k_pool[pages].permute(1, 0, 2, 3).reshape(kv_heads, -1, k_pool.shape[3])[:, lo:hi].float()
             keys = entries[..., :dim]
             vals = (entries[..., dim:] if v_pool is None
-                    else v_pool[pages].permute(1, 0, 2, 3).reshape(kv_heads, -1, vdim)[:, : pos + 1].float())
+                    else v_pool[pages].permute(1, 0, 2, 3).reshape(kv_heads, -1, vdim)[:, lo:hi].float())
+            assert (pages[lo // page_size :] >= 0).all(), "a page inside the window was given back"
             q = qkv[t, : heads * dim].float().reshape(heads, dim)
             for h in range(heads):
                 s = (keys[h // group] @ q[h]) * scale
+                if softcap:
+                    s = softcap * torch.tanh(s / softcap)
                 m = torch.clamp(s.max(), min=0.0) if sink else s.max()
                 e = torch.exp(s - m)
                 out[t, h * vdim : (h + 1) * vdim] = ((e / (e.sum() + (torch.exp(-m) if sink else 0.0))) @ vals[h // group]).to(qkv.dtype)
         return out
+
+    # ---- a 32-bit stream with root-mean-square norms, a hashed pair embedding, token inputs
+    def pair_embedding(self, table, pairs, ids, positions, token_row, q_indptr, slots, state, buckets, mul_prev, mul_cur):
+        T = ids.numel()
+        out = torch.zeros(T, table.shape[1], dtype=torch.float32)
+        for t in range(T):
+            r = int(token_row[t])
+            if int(positions[t]) <= 0:
+                row = buckets
+            else:
+                prev = int(ids[t - 1]) if t > int(q_indptr[r]) else int(state[int(slots[r]), 0])
+                row = (prev * mul_prev + int(ids[t]) * mul_cur) % buckets
+            out[t] = table[int(ids[t])].float() + pairs[row].float()
+        return out
+
+    def last_token_store(self, ids, q_indptr, slots, state):
+        for r in range(slots.numel()):
+            lo, hi = int(q_indptr[r]), int(q_indptr[r + 1])
+            if hi > lo:
+                state[int(slots[r]), 0] = int(ids[hi - 1])
+
+    def wide_rms_norm(self, stream, w, eps, out_dtype, addend=None, extra=None, rows=None):
+        s = stream
+        if addend is not None:
+            s = s + addend.float()
+        if extra is not None:
+            s = s + extra
+        if rows is None and s is not stream:
+            stream.copy_(s)
+        if rows is not None:
+            s = s[rows.long()]
+        if w is not None:
+            s = s * torch.rsqrt((s * s).mean(-1, keepdim=True) + eps) * w.float()
+        return s.to(out_dtype)
+
+    def normed_mean(self, xs, ws, eps):
+        acc = 0
+        for x, w in zip(xs, ws):
+            xf = x.float()
+            acc = acc + xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + eps) * w.float()
+        return (acc / len(xs)).to(xs[0].dtype)
+
+    def add_bias_(self, y, bias):
+        y += bias.to(y.dtype)
+        return y
+
+    def gelu_mul_rows(self, gate, table, ids):
+        g = gate.float()
+        act = 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3)))
+        return (act * table[ids.long()].float()).to(gate.dtype)
+
+    # ---- the gated linear recurrence
+    def gated_recurrence_scan(self, u, gates, yx, gate_bias, decay, state, q_indptr, slots, width, blocks):
+        T, bw = u.shape[0], width // blocks
+        out = torch.zeros(T, width, dtype=u.dtype)
+        arg = gates.float() + gate_bias[:, None, :]                      # [blocks, T, 2 bw]
+        r = torch.sigmoid(arg[:, :, :bw]).permute(1, 0, 2).reshape(T, width)
+        i = torch.sigmoid(arg[:, :, bw:]).permute(1, 0, 2).reshape(T, width)
+        a = torch.exp(-decay * r)
+        drive = torch.sqrt(1 - a * a) * i * u.float()
+        y = yx[:, :width].float()
+        y = 0.5 * y * (1 + torch.tanh(math.sqrt(2 / math.pi) * (y + 0.044715 * y ** 3)))
+        for row in range(slots.numel()):
+            lo, hi = int(q_indptr[row]), int(q_indptr[row + 1])
+            S = state[int(slots[row]), :width]
+            for t in range(lo, hi):
+                S.copy_(a[t] * S + drive[t])
+                out[t] = (S * y[t]).to(u.dtype)
+        return out
+
+    # ---- the matrix memory
+    def matrix_memory_scan(self, qkvg, gates, state, q_indptr, slots, heads, dim, vdim, cap, floor):
+        T = qkvg.shape[0]
+        QK = heads * dim
+        q = qkvg[:, :QK].float().reshape(T, heads, dim) * dim ** -0.5
+        k = qkvg[:, QK : 2 * QK].float().reshape(T, heads, dim)
+        v = qkvg[:, 2 * QK : 2 * QK + heads * vdim].float().reshape(T, heads, vdim)
+        gi = cap * torch.tanh(gates[:, :heads] / cap)
+        gf = torch.nn.functional.logsigmoid(cap * torch.tanh(gates[:, heads:] / cap))
+        out = torch.zeros(T, heads * vdim, dtype=torch.float32)
+        per = dim * vdim + dim + 1
+        for row in range(slots.numel()):
+            lo, hi = int(q_indptr[row]), int(q_indptr[row + 1])
+            st = state[int(slots[row])].view(heads, per)
+            for t in range(lo, hi):
+                S, n, m = st[:, : dim * vdim].reshape(heads, dim, vdim), st[:, dim * vdim : dim * vdim + dim], st[:, -1]
+                new = torch.maximum(gf[t] + m, gi[t])
+                keep, take = torch.exp(gf[t] + m - new), torch.exp(gi[t] - new)
+                S = keep[:, None, None] * S + take[:, None, None] * k[t][:, :, None] * v[t][:, None, :]
+                n = keep[:, None] * n + take[:, None] * k[t]
+                num = torch.einsum("hdv,hd->hv", S, q[t])
+                den = torch.maximum((n * q[t]).sum(-1).abs(), torch.exp(-new)) + floor
+                out[t] = (num / den[:, None]).reshape(-1)
+                st.copy_(torch.cat([S.reshape(heads, -1), n, new[:, None]], dim=1))
+        return out
+
+    def head_norm_gate(self, o, u, col, w, heads, eps, out_dtype):
+        T, V = o.shape
+        x = o.reshape(T, heads, V // heads)
+        x = (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps)).reshape(T, V) * w.float()
+        return (x * torch.sigmoid(u[:, col : col + V].float())).to(out_dtype)
 
     # ---- the selective scan
     def mamba1_scan(self, xc, dt, dbc, xz, dt_bias, a, d, state, q_indptr, slots, inner, N, R):
