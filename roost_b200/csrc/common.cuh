@@ -113,6 +113,24 @@ __device__ __forceinline__ float gate_fn(float g, float u, int act, float limit)
   return g / (1.0f + expf(-g)) * u;
 }
 
+// exp(x) for x <= 0 to about one unit in the last place: x = j ln2 + r with ln2 in two parts, a degree-7 polynomial in r.
+__device__ __forceinline__ float exp_nearest(float x) {
+  if (x < -87.0f) return 0.f;
+  const float j = rintf(x * 1.44269504088896341f);
+  float r = fmaf(j, -0.693359375f, x);
+  r = fmaf(j, 2.12194440e-4f, r);
+  float p = 1.9875691500e-4f;
+  p = fmaf(p, r, 1.3981999507e-3f);
+  p = fmaf(p, r, 8.3334519073e-3f);
+  p = fmaf(p, r, 4.1665795894e-2f);
+  p = fmaf(p, r, 1.6666665459e-1f);
+  p = fmaf(p, r, 5.0000001201e-1f);
+  const float y = fmaf(p * r, r, r) + 1.0f;
+  return y * __int_as_float(((int)j + 127) << 23);
+}
+
+__device__ __forceinline__ float gelu_tanh_f(float z) { return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+
 // Weight vectors (norm weights) may be stored in either dtype whatever the activations are.
 __device__ __forceinline__ float load_w(const void* w, int i, int wdtype) {
   return wdtype == ROOST_F32 ? reinterpret_cast<const float*>(w)[i]

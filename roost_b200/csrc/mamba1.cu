@@ -28,21 +28,6 @@ constexpr int kM1Chunk = 8;          // tokens staged at once by a block that wa
 constexpr int kM1ChunkLong = 32;     // ... and by a block that walks many tokens: four times fewer waits for the staged loads
 constexpr int kM1PerLane = 8;
 
-// exp(x) for x <= 0 to about one unit in the last place: x = j ln2 + r with ln2 in two parts, a degree-7 polynomial in r.
-__device__ __forceinline__ float exp_nearest(float x) {
-  if (x < -87.0f) return 0.f;
-  const float j = rintf(x * 1.44269504088896341f);
-  float r = fmaf(j, -0.693359375f, x);
-  r = fmaf(j, 2.12194440e-4f, r);
-  float p = 1.9875691500e-4f;
-  p = fmaf(p, r, 1.3981999507e-3f);
-  p = fmaf(p, r, 8.3334519073e-3f);
-  p = fmaf(p, r, 4.1665795894e-2f);
-  p = fmaf(p, r, 1.6666665459e-1f);
-  p = fmaf(p, r, 5.0000001201e-1f);
-  const float y = fmaf(p * r, r, r) + 1.0f;
-  return y * __int_as_float(((int)j + 127) << 23);
-}
 template <typename T>
 __device__ __forceinline__ float decay_exp(float x) { return expf(x); }
 template <>

@@ -23,7 +23,7 @@ template <typename T>
 __global__ void mamba2_conv_kernel(const T* __restrict__ u, int64_t ld, int col, T* __restrict__ out, const float* __restrict__ w,
                                    const float* __restrict__ bias, const float* __restrict__ state, int64_t state_stride, int conv_off,
                                    const int32_t* __restrict__ token_row, const int32_t* __restrict__ q_indptr,
-                                   const int32_t* __restrict__ slots, int channels, int taps) {
+                                   const int32_t* __restrict__ slots, int channels, int taps, int act) {
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -38,7 +38,7 @@ __global__ void mamba2_conv_kernel(const T* __restrict__ u, int64_t ld, int col,
     const float v = i >= start ? to_float(u[(size_t)i * ld + col + c]) : st[(size_t)(i - start + taps - 1) * channels + c];
     acc = fmaf(w[(size_t)c * taps + k], v, acc);
   }
-  out[(size_t)t * channels + c] = from_float<T>(silu_f(acc));
+  out[(size_t)t * channels + c] = from_float<T>(act ? silu_f(acc) : acc);
 }
 
 template <typename T>
@@ -373,13 +373,13 @@ using namespace roost;
 
 extern "C" int roost_mamba2_conv(const void* u, int64_t ld, int col, void* out, const float* w, const float* bias, const float* state,
                                  int64_t state_stride, int conv_off, const int32_t* token_row, const int32_t* q_indptr, const int32_t* slots,
-                                 int tokens, int channels, int taps, int dtype, roost_stream_t stream) {
+                                 int tokens, int channels, int taps, int act, int dtype, roost_stream_t stream) {
   ROOST_REQUIRE(tokens >= 0 && channels > 0 && taps > 0 && col >= 0 && ld >= col + channels, "mamba2_conv: sizes do not fit");
   if (tokens == 0) return ROOST_OK;
   dim3 grid(tokens, (channels + 255) / 256);
   if (grid.y > 65535) return fail(ROOST_ERR_UNSUPPORTED, "mamba2_conv: too many channels");
   ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(mamba2_conv_kernel<T>, grid, dim3(256), 0, (cudaStream_t)stream, (const T*)u, ld, col, (T*)out, w,
-                                               bias, state, state_stride, conv_off, token_row, q_indptr, slots, channels, taps));
+                                               bias, state, state_stride, conv_off, token_row, q_indptr, slots, channels, taps, act));
   return check_launch("mamba2_conv");
 }
 

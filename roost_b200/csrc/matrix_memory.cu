@@ -1,0 +1,202 @@
+// A matrix memory a head with exponential gates (the mLSTM cell), in 32-bit arithmetic.
+//
+// Per (row, head), for the row's tokens in order, with q, k (dim numbers) and v (vdim numbers) from the row [q | k | v | ...] of
+// the input projection and the two gates' arguments a head as 32-bit sums [i of every head | f of every head]:
+//   i = c tanh(gi / c), f = logsigmoid(c tanh(gf / c)), m' = max(f + m, i), keep = exp(f + m - m'), take = exp(i - m'),
+//   S <- keep S + take k v^T, n <- keep n + take k, o = S^T (q / sqrt(dim)) / (max(|n . q / sqrt(dim)|, exp(-m')) + floor).
+// The slot holds, head after head, [S: dim x vdim | n: dim | m].
+//
+// scan: one warp (a block) per (row, head, 32 columns of S). A lane keeps its column of S in registers (dim up to 128) or in
+// shared memory (beyond), and the entries lane, lane + 32, ... of n; a token's (take k, q) are staged in shared memory once
+// and read by all lanes; n . q is a warp sum. The next token's q, k, v and gates are loaded while the current one is
+// multiplied. Every warp of a head keeps n and m for itself; the first writes them back.
+//
+// head_norm_gate: per token and head, o / sqrt(mean(o^2) + eps) * w * sigmoid(g), rounded once.
+#include "common.cuh"
+
+namespace roost {
+
+template <typename T>
+__device__ __forceinline__ float memory_exp(float x) { return expf(x); }
+template <>
+__device__ __forceinline__ float memory_exp<float>(float x) { return exp_nearest(x); }
+
+__device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+// DREG > 0: S in registers, dim <= DREG. DREG == 0: S in shared memory after the staging area, [dim][32].
+template <typename T, int DREG>
+__global__ void __launch_bounds__(32) matrix_memory_scan_kernel(const T* __restrict__ qkv, int64_t ld, const float* __restrict__ gates,
+                                                               float* __restrict__ out, float* state, int64_t state_stride,
+                                                               const int32_t* __restrict__ q_indptr, const int32_t* __restrict__ slots, int heads,
+                                                               int dim, int vdim, float cap, float floor_) {
+  extern __shared__ float sm[];      // two staging slots of dim (take k, q) pairs; then S when it does not live in registers
+  constexpr int NREG = DREG > 0 ? DREG : 1;
+  constexpr int NN = DREG > 0 ? DREG / 32 : 32;          // entries of n a lane keeps (dim <= 1024 in shared-memory form)
+  pdl_launch_dependents();
+  const int r = blockIdx.x, h = blockIdx.y, slice = blockIdx.z;
+  const int lane = threadIdx.x;
+  const int col = slice * 32 + lane;
+  const bool live = col < vdim;
+  const int start = q_indptr[r], end = q_indptr[r + 1];
+  float* hs = state + (size_t)slots[r] * state_stride + (size_t)h * ((size_t)dim * vdim + dim + 1);
+  float* S_sm = sm + 4 * dim + lane;                       // [dim][32], used when DREG == 0
+  const float inv_cap = 1.0f / cap, q_scale = rsqrtf((float)dim);
+  const int QK = heads * dim;
+  pdl_wait();
+  if (end <= start) return;
+  float S[NREG], n[NN];
+  if (DREG > 0) {
+#pragma unroll
+    for (int d = 0; d < NREG; ++d) S[d] = (live && d < dim) ? hs[(size_t)d * vdim + col] : 0.f;
+  } else {
+    for (int d = 0; d < dim; ++d) S_sm[(size_t)d * 32] = live ? hs[(size_t)d * vdim + col] : 0.f;
+  }
+#pragma unroll
+  for (int i = 0; i < NN; ++i) {
+    const int d = lane + 32 * i;
+    n[i] = d < dim ? hs[(size_t)dim * vdim + d] : 0.f;
+  }
+  float m = hs[(size_t)dim * vdim + dim];
+
+  // the next token's inputs, loaded one token ahead
+  float nk[NN], nq[NN], nv, ngi, ngf;
+  auto load = [&](int t) {
+    const T* row = qkv + (size_t)t * ld;
+#pragma unroll
+    for (int i = 0; i < NN; ++i) {
+      const int d = lane + 32 * i;
+      nq[i] = d < dim ? to_float(row[(size_t)h * dim + d]) * q_scale : 0.f;
+      nk[i] = d < dim ? to_float(row[QK + (size_t)h * dim + d]) : 0.f;
+    }
+    nv = live ? to_float(row[2 * QK + (size_t)h * vdim + col]) : 0.f;
+    ngi = gates[(size_t)t * 2 * heads + h];
+    ngf = gates[(size_t)t * 2 * heads + heads + h];
+  };
+  load(start);
+  for (int t = start; t < end; ++t) {
+    const float gi = cap * tanhf(ngi * inv_cap);
+    const float gf = log_sigmoid_f(cap * tanhf(ngf * inv_cap));
+    const float m_new = fmaxf(gf + m, gi);
+    const float keep = memory_exp<T>(gf + m - m_new), take = memory_exp<T>(gi - m_new);
+    m = m_new;
+    float2* stage = reinterpret_cast<float2*>(sm) + (size_t)(t & 1) * dim;
+    float nq_part = 0.f;
+#pragma unroll
+    for (int i = 0; i < NN; ++i) {
+      const int d = lane + 32 * i;
+      if (d < dim) {
+        const float tk = take * nk[i];
+        stage[d] = make_float2(tk, nq[i]);
+        n[i] = fmaf(keep, n[i], tk);
+        nq_part = fmaf(n[i], nq[i], nq_part);
+      }
+    }
+    const float v = nv;
+    if (t + 1 < end) load(t + 1);
+    __syncwarp();
+    float num = 0.f;
+    if (DREG > 0) {
+#pragma unroll
+      for (int d = 0; d < NREG; ++d) {
+        if (d < dim) {
+          const float2 kq = stage[d];
+          S[d] = fmaf(keep, S[d], kq.x * v);
+          num = fmaf(S[d], kq.y, num);
+        }
+      }
+    } else {
+      for (int d = 0; d < dim; ++d) {
+        const float2 kq = stage[d];
+        const float s = fmaf(keep, S_sm[(size_t)d * 32], kq.x * v);
+        S_sm[(size_t)d * 32] = s;
+        num = fmaf(s, kq.y, num);
+      }
+    }
+    const float den = fmaxf(fabsf(warp_sum(nq_part)), memory_exp<T>(-m)) + floor_;
+    if (live) out[(size_t)t * heads * vdim + (size_t)h * vdim + col] = num / den;
+  }
+  if (live) {
+    if (DREG > 0) {
+#pragma unroll
+      for (int d = 0; d < NREG; ++d)
+        if (d < dim) hs[(size_t)d * vdim + col] = S[d];
+    } else {
+      for (int d = 0; d < dim; ++d) hs[(size_t)d * vdim + col] = S_sm[(size_t)d * 32];
+    }
+  }
+  if (slice == 0) {
+#pragma unroll
+    for (int i = 0; i < NN; ++i) {
+      const int d = lane + 32 * i;
+      if (d < dim) hs[(size_t)dim * vdim + d] = n[i];
+    }
+    if (lane == 0) hs[(size_t)dim * vdim + dim] = m;
+  }
+}
+
+template <typename T>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ u, int64_t ld_u, int col, const float* __restrict__ w,
+                                      T* __restrict__ out, int heads, int vdim, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int h = warp; h < heads; h += nwarps) {
+    const float* x = o + (t * heads + h) * vdim;
+    float ss = 0.f;
+    for (int i = lane; i < vdim; i += 32) ss = fmaf(x[i], x[i], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
+    for (int i = lane; i < vdim; i += 32) {
+      const size_t c = (size_t)h * vdim + i;
+      const float g = to_float(u[t * ld_u + col + c]);
+      out[t * heads * vdim + c] = from_float<T>(x[i] * inv * w[c] / (1.0f + expf(-g)));
+    }
+  }
+}
+
+}  // namespace roost
+
+using namespace roost;
+
+extern "C" int roost_matrix_memory_scan(const void* qkv, int64_t ld, const float* gates, float* out, float* state, int64_t state_stride,
+                                        const int32_t* q_indptr, const int32_t* slots, int rows, int heads, int dim, int vdim, float cap,
+                                        float floor_, int dtype, roost_stream_t stream) {
+  ROOST_REQUIRE(rows >= 0 && heads > 0 && dim > 0 && vdim > 0 && cap > 0.f && floor_ >= 0.f, "matrix_memory_scan: sizes and the cap must be positive");
+  ROOST_REQUIRE(qkv && gates && out && state && q_indptr && slots, "matrix_memory_scan: a pointer is null");
+  ROOST_REQUIRE(ld >= (int64_t)heads * (2 * dim + vdim) && state_stride >= (int64_t)heads * ((int64_t)dim * vdim + dim + 1),
+                "matrix_memory_scan: a row or a slot is too narrow");
+  if (dim > 1024) return fail(ROOST_ERR_UNSUPPORTED, "matrix_memory_scan: heads of more than 1024 keys");
+  const int slices = (vdim + 31) / 32;
+  if (heads > 65535 || slices > 65535) return fail(ROOST_ERR_UNSUPPORTED, "matrix_memory_scan: too many heads or values");
+  if (rows == 0) return ROOST_OK;
+  dim3 grid(rows, heads, slices);
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t stage = (size_t)4 * dim * sizeof(float);
+#define ROOST_MM_SCAN(DREG, SMEM)                                                                                                                 \
+  do {                                                                                                                                            \
+    auto kernel = matrix_memory_scan_kernel<T, DREG>;                                                                                             \
+    if ((SMEM) > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SMEM));                               \
+    launch_kernel(kernel, grid, dim3(32), (SMEM), s, (const T*)qkv, ld, gates, out, state, state_stride, q_indptr, slots, heads, dim, vdim, cap,  \
+                  floor_);                                                                                                                        \
+  } while (0)
+  ROOST_DISPATCH_DTYPE(dtype, T, {
+    if (dim <= 32) ROOST_MM_SCAN(32, stage);
+    else if (dim <= 64) ROOST_MM_SCAN(64, stage);
+    else if (dim <= 128) ROOST_MM_SCAN(128, stage);
+    else ROOST_MM_SCAN(0, stage + (size_t)dim * 32 * sizeof(float));
+  });
+#undef ROOST_MM_SCAN
+  return check_launch("matrix_memory_scan");
+}
+
+extern "C" int roost_head_norm_gate(const float* o, const void* u, int64_t ld_u, int col, const float* w, void* out, int tokens, int heads, int vdim,
+                                    float eps, int dtype, roost_stream_t stream) {
+  ROOST_REQUIRE(tokens >= 0 && heads > 0 && vdim > 0 && eps > 0.f && col >= 0 && ld_u >= col + (int64_t)heads * vdim, "head_norm_gate: sizes do not fit");
+  ROOST_REQUIRE(o && u && w && out, "head_norm_gate: a pointer is null");
+  if (tokens == 0) return ROOST_OK;
+  const int threads = heads >= 8 ? 256 : (heads >= 4 ? 128 : 32 * heads);
+  ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(head_norm_gate_kernel<T>, dim3(tokens), dim3(threads), 0, (cudaStream_t)stream, o, (const T*)u, ld_u, col,
+                                               w, (T*)out, heads, vdim, eps));
+  return check_launch("head_norm_gate");
+}

@@ -17,7 +17,7 @@
 extern "C" {
 #endif
 
-#define ROOST_ABI_VERSION 13
+#define ROOST_ABI_VERSION 14
 
 #define ROOST_OK 0
 #define ROOST_ERR_INVALID 1      /* an argument is out of range or inconsistent; nothing was launched */
@@ -301,7 +301,7 @@ int roost_latent_attention_tc(const void* q_latent, const void* q, void* out, co
 /* ---- the Mamba-2 recurrence (mamba2.cu; the layout of a state slot and the formulas are at the top of that file) ---- */
 int roost_mamba2_conv(const void* u, int64_t ld, int col, void* out, const float* w, const float* bias, const float* state,
                       int64_t state_stride, int conv_off, const int32_t* token_row, const int32_t* q_indptr, const int32_t* slots,
-                      int tokens, int channels, int taps, int dtype, roost_stream_t stream);
+                      int tokens, int channels, int taps, int act, int dtype, roost_stream_t stream);   /* act != 0: SiLU of the sum */
 int roost_mamba2_conv_state(const void* u, int64_t ld, int col, float* state, int64_t state_stride, int conv_off,
                             const int32_t* q_indptr, const int32_t* slots, int rows, int channels, int taps, int dtype,
                             roost_stream_t stream);
@@ -369,14 +369,14 @@ int roost_gated_act_mul(const void* x, void* out, int tokens, int inter, int blo
  * entry from k_base and v_base. */
 int roost_sink_attention_prepare(void* qkv, int64_t ld, void* q_out, void* k_base, void* v_base, int entry, const double* inv_freq,
                                  const int32_t* positions, const int32_t* slot_mapping, int tokens, int heads, int kv_heads, int dim, int vdim,
-                                 int rot_dims, float eps, int page_size, int dtype, roost_stream_t stream);
+                                 int rot_dims, float eps, int page_size, int halves, int dtype, roost_stream_t stream);
 /* out [tokens, heads * vdim]. sink != 0: one is added to the softmax's denominator. splits > 1: a token's key tiles of 32 are
  * dealt in ranges of tiles_per_split to `splits` blocks whose partials (part: float[tokens * heads * splits * (vdim + 2)]) a
  * second kernel combines. */
 int roost_sink_attention(const void* qkv, int64_t ld, void* out, float* part, const void* k_base, const void* v_base, int entry,
                          const int32_t* positions, const int32_t* token_row, const int32_t* kv_indptr, const int32_t* kv_indices, int tokens,
                          int heads, int kv_heads, int dim, int vdim, int page_size, float scale, int sink, int splits, int tiles_per_split,
-                         int dtype, roost_stream_t stream);
+                         int window, float softcap, int dtype, roost_stream_t stream);   /* window 0: every earlier key; softcap 0: none */
 
 /* ---- the Mamba selective scan (mamba1.cu) ---- */
 /* Per (row, channel): dt = softplus(dt_raw + dt_bias); S <- exp(dt a_neg) S + dt x B; y = S . C + d_skip x; out = y silu(z). xc
@@ -389,6 +389,42 @@ int roost_mamba1_scan(const void* xc, const float* dt_raw, const void* dbc, int6
                       const float* dt_bias, const float* a_neg, const float* d_skip, float* state, int64_t state_stride,
                       const int32_t* q_indptr, const int32_t* slots, int rows, int tokens, int inner, int n_state, int dt_rank,
                       float* ws_state, float* ws_dt, int dtype, roost_stream_t stream);
+
+/* ---- a 32-bit stream with root-mean-square norms, a hashed pair embedding, token inputs (wide_stream.cu) ---- */
+/* s = stream + addend (activation dtype, may be null) + extra (float, may be null), written back unless `rows` gathers; out = s /
+ * sqrt(mean(s^2) + eps) * w, or s where w is null. */
+int roost_wide_rms_norm(float* stream, const void* addend, const float* extra, const float* w, void* out, const int32_t* rows, int n_out,
+                        int hidden, float eps, int dtype, roost_stream_t stream_handle);
+/* out = mean over the n (1 to 4) branches of xs[b] / sqrt(mean(xs[b]^2) + eps) * ws[b]. */
+int roost_normed_mean(const void* const* xs, const float* const* ws, int n, void* out, int tokens, int hidden, float eps, int dtype,
+                      roost_stream_t stream);
+/* out[t] = table[ids[t]] + pairs[row]: row = (previous id * mul_prev + id * mul_cur) mod buckets, `buckets` at position <= 0; the id
+ * before a row's first token of the step is state[slots[row]]. */
+int roost_pair_embedding(const void* table, const void* pairs, const int32_t* ids, const int32_t* positions, const int32_t* token_row,
+                         const int32_t* q_indptr, const int32_t* slots, const int32_t* state, float* out, int tokens, int hidden, int vocab,
+                         int buckets, int mul_prev, int mul_cur, int dtype, roost_stream_t stream);
+/* state[slots[r]] = the last id of row r (rows without tokens keep theirs). */
+int roost_last_token_store(const int32_t* ids, const int32_t* q_indptr, const int32_t* slots, int32_t* state, int rows, roost_stream_t stream);
+int roost_add_bias(float* y, const float* bias, int rows, int width, roost_stream_t stream);
+/* out[t] = gelu_tanh(gate[t]) * table[ids[t]]. */
+int roost_gelu_mul_rows(const void* gate, const void* table, const int32_t* ids, void* out, int tokens, int width, int vocab, int dtype,
+                        roost_stream_t stream);
+
+/* ---- the gated linear recurrence (gated_recurrence.cu) ---- */
+/* u [tokens, width]; gates float[blocks][tokens][2 * width / blocks]; yx rows [y | ...]; state slots [S: width | ...]. */
+int roost_gated_recurrence_scan(const void* u, const float* gates, const void* yx, int64_t ld_yx, void* out, const float* gate_bias,
+                                const float* decay, float* state, int64_t state_stride, const int32_t* q_indptr, const int32_t* slots,
+                                int rows, int tokens, int width, int blocks, int dtype, roost_stream_t stream);
+
+/* ---- the matrix memory (matrix_memory.cu) ---- */
+/* qkv rows [q: heads x dim | k: heads x dim | v: heads x vdim | ...]; gates float[tokens][i a head | f a head]; out float[tokens,
+ * heads * vdim]; state slots, head after head, [S: dim x vdim | n: dim | m]. */
+int roost_matrix_memory_scan(const void* qkv, int64_t ld, const float* gates, float* out, float* state, int64_t state_stride,
+                             const int32_t* q_indptr, const int32_t* slots, int rows, int heads, int dim, int vdim, float cap, float floor_,
+                             int dtype, roost_stream_t stream);
+/* out = o / sqrt(mean over a head of o^2 + eps) * w * sigmoid(u[:, col:]). */
+int roost_head_norm_gate(const float* o, const void* u, int64_t ld_u, int col, const float* w, void* out, int tokens, int heads, int vdim,
+                         float eps, int dtype, roost_stream_t stream);
 
 #ifdef __cplusplus
 }

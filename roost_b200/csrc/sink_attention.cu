@@ -3,7 +3,8 @@
 //
 //   prepare:   per token, on a row [q heads | k heads | v heads] of the fused projection: every query and key head has its
 //              first rot_dims elements turned in interleaved pairs, (u, v) at (2i, 2i+1) -> (u cos a - v sin a, v cos a + u sin a)
-//              with a = position * inv_freq[i] formed in double and reduced to [-pi, pi]; then, with eps > 0, the head is
+//              with a = position * inv_freq[i] formed in double and reduced to [-pi, pi] (with `halves` the pair is
+//              (i, i + rot_dims / 2) instead); then, with eps > 0, the head is
 //              divided by sqrt(mean(x^2) + eps) (no weight). Queries are written back in place (or, with q_out, to a dense
 //              [tokens, heads, dim] tensor of their own, which the tensor-core attention kernels read), keys and values go to the
 //              token's cache slot (slot -1: nothing is written). The cache entry of (page, kv head, offset) starts at
@@ -15,6 +16,9 @@
 //              maximum starts at 0 and the denominator at 1. A token's tiles may be dealt to several blocks in ranges
 //              (split z of Z takes tiles [z n, (z + 1) n), n from the step's bound on lengths); the partial sums, maxima and
 //              denominators are then combined in split order by a second kernel. A padding token (position -1) is skipped.
+//              With a window a query at position p sees the keys p - window + 1 .. p: its tiles start at the tile of the first
+//              such key, and no page before that tile's is looked up (the cache may have given it back). With a cap c a scaled
+//              score s becomes c tanh(s / c).
 #include "common.cuh"
 
 namespace roost {
@@ -26,7 +30,8 @@ constexpr int kSaMaxDim = 512;
 template <typename T>
 __global__ void __launch_bounds__(128) sink_prepare_kernel(T* qkv, int64_t ld, T* q_out, T* k_base, T* v_base, int entry, const double* __restrict__ inv_freq,
                                                           const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping,
-                                                          int heads, int kv_heads, int dim, int vdim, int rot_dims, float eps, int page_size) {
+                                                          int heads, int kv_heads, int dim, int vdim, int rot_dims, float eps, int page_size,
+                                                          int halves) {
   extern __shared__ float sm[];      // rot_dims/2 cosines, rot_dims/2 sines
   const int half = rot_dims / 2;
   float* cs = sm;
@@ -55,8 +60,10 @@ __global__ void __launch_bounds__(128) sink_prepare_kernel(T* qkv, int64_t ld, T
       const int j = c * 32 + lane;
       a[c] = b[c] = 0.f;
       if (j < pairs) {
-        float u = to_float(x[2 * j]);
-        float v = 2 * j + 1 < dim ? to_float(x[2 * j + 1]) : 0.f;
+        const int ia = halves && j < half ? j : 2 * j;                 // the pair's elements: (j, j + half) among the rotated ones
+        const int ib = halves && j < half ? j + half : 2 * j + 1;      // with `halves`, neighbours otherwise and after them
+        float u = to_float(x[ia]);
+        float v = ib < dim ? to_float(x[ib]) : 0.f;
         if (j < half) {
           const float ru = u * cs[j] - v * sn[j], rv = v * cs[j] + u * sn[j];
           u = ru;
@@ -78,8 +85,10 @@ __global__ void __launch_bounds__(128) sink_prepare_kernel(T* qkv, int64_t ld, T
     for (int c = 0; c < kSaMaxDim / 64; ++c) {
       const int j = c * 32 + lane;
       if (j < pairs) {
-        dst[2 * j] = from_float<T>(a[c] * inv);
-        if (2 * j + 1 < dim) dst[2 * j + 1] = from_float<T>(b[c] * inv);
+        const int ia = halves && j < half ? j : 2 * j;
+        const int ib = halves && j < half ? j + half : 2 * j + 1;
+        dst[ia] = from_float<T>(a[c] * inv);
+        if (ib < dim) dst[ib] = from_float<T>(b[c] * inv);
       }
     }
   }
@@ -97,7 +106,7 @@ __global__ void __launch_bounds__(kSaWarps * 32) sink_attention_kernel(const T* 
                                                                      const int32_t* __restrict__ positions, const int32_t* __restrict__ token_row,
                                                                      const int32_t* __restrict__ kv_indptr, const int32_t* __restrict__ kv_indices,
                                                                      int heads, int kv_heads, int dim, int vdim, int page_size, float scale, int sink,
-                                                                     int splits, int tiles_per_split) {
+                                                                     int splits, int tiles_per_split, int window, float softcap) {
   extern __shared__ float sm[];
   float* ks = sm;                                          // [tile][dim + 1]
   float* vs = ks + (size_t)kSaTile * (dim + 1);            // [tile][vdim]
@@ -130,8 +139,10 @@ __global__ void __launch_bounds__(kSaWarps * 32) sink_attention_kernel(const T* 
   float acc[kSaMaxDim / 32];
 #pragma unroll
   for (int c = 0; c < kSaMaxDim / 32; ++c) acc[c] = 0.f;
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;     // the first key the query sees
   const int n_tiles = pos / kSaTile + 1;
-  const int first = z * tiles_per_split, last = min(n_tiles, first + tiles_per_split);
+  const int first = lo / kSaTile + z * tiles_per_split, last = min(n_tiles, first + tiles_per_split);
+  const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
   for (int tile = first; tile < last; ++tile) {
     const int k0 = tile * kSaTile;
     __syncthreads();
@@ -139,7 +150,7 @@ __global__ void __launch_bounds__(kSaWarps * 32) sink_attention_kernel(const T* 
       const int kp = k0 + kk;
       float* kd = ks + (size_t)kk * (dim + 1);
       float* vd = vs + (size_t)kk * vdim;
-      if (kp <= pos) {
+      if (kp <= pos && kp >= lo) {
         const size_t at = (((size_t)pages[kp / page_size] * kv_heads + g) * page_size + kp % page_size) * entry;
         const T* kr = k_base + at;
         const T* vr = v_base + at;
@@ -167,7 +178,9 @@ __global__ void __launch_bounds__(kSaWarps * 32) sink_attention_kernel(const T* 
     } else {
       for (int i = 0; i < dim; ++i) s = fmaf(qw[i], kr[i], s);
     }
-    s = k0 + lane <= pos ? s * scale : -INFINITY;
+    s *= scale;
+    if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
+    if (k0 + lane > pos || k0 + lane < lo) s = -INFINITY;
     const float m_new = fmaxf(m, warp_max(s));
     const float p = s > -INFINITY ? expf(s - m_new) : 0.f;
     const float keep = m > -INFINITY ? expf(m - m_new) : 0.f;
@@ -251,7 +264,7 @@ using namespace roost;
 
 extern "C" int roost_sink_attention_prepare(void* qkv, int64_t ld, void* q_out, void* k_base, void* v_base, int entry, const double* inv_freq,
                                             const int32_t* positions, const int32_t* slot_mapping, int tokens, int heads, int kv_heads, int dim,
-                                            int vdim, int rot_dims, float eps, int page_size, int dtype, roost_stream_t stream) {
+                                            int vdim, int rot_dims, float eps, int page_size, int halves, int dtype, roost_stream_t stream) {
   ROOST_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 && page_size > 0, "sink_attention_prepare: sizes must be positive");
   ROOST_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dim, "sink_attention_prepare: the rotated width must be even and at most dim");
   ROOST_REQUIRE(qkv && k_base && v_base && positions && slot_mapping && (rot_dims == 0 || inv_freq), "sink_attention_prepare: a pointer is null");
@@ -263,16 +276,17 @@ extern "C" int roost_sink_attention_prepare(void* qkv, int64_t ld, void* q_out, 
   // four warps a token: measured faster than a warp a head (sixteen warps: 30.7 against 19.6 us at 2,048 tokens of 16 + 4 heads of 64)
   ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(sink_prepare_kernel<T>, dim3(tokens), dim3(128), smem, (cudaStream_t)stream, (T*)qkv, ld, (T*)q_out, (T*)k_base,
                                                (T*)v_base, entry, inv_freq, positions, slot_mapping, heads, kv_heads, dim, vdim, rot_dims, eps,
-                                               page_size));
+                                               page_size, halves));
   return check_launch("sink_attention_prepare");
 }
 
 extern "C" int roost_sink_attention(const void* qkv, int64_t ld, void* out, float* part, const void* k_base, const void* v_base, int entry,
                                     const int32_t* positions, const int32_t* token_row, const int32_t* kv_indptr, const int32_t* kv_indices,
                                     int tokens, int heads, int kv_heads, int dim, int vdim, int page_size, float scale, int sink, int splits,
-                                    int tiles_per_split, int dtype, roost_stream_t stream) {
+                                    int tiles_per_split, int window, float softcap, int dtype, roost_stream_t stream) {
   ROOST_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 && page_size > 0, "sink_attention: sizes must be positive");
   ROOST_REQUIRE(heads % kv_heads == 0, "sink_attention: the query heads are no multiple of the key/value heads");
+  ROOST_REQUIRE(window >= 0 && softcap >= 0.f, "sink_attention: the window and the scores' cap cannot be negative");
   ROOST_REQUIRE(splits >= 1 && tiles_per_split >= 1 && (splits == 1 || part != nullptr), "sink_attention: splits need a workspace for their partials");
   if (dim > kSaMaxDim || vdim > kSaMaxDim) return fail(ROOST_ERR_UNSUPPORTED, "sink_attention: heads or values beyond 512 numbers");
   const int group = heads / kv_heads;
@@ -286,7 +300,7 @@ extern "C" int roost_sink_attention(const void* qkv, int64_t ld, void* out, floa
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_kernel(kernel, grid, dim3(kSaWarps * 32), smem, (cudaStream_t)stream, (const T*)qkv, ld, (T*)out, splits > 1 ? part : (float*)nullptr,
                   (const T*)k_base, (const T*)v_base, entry, positions, token_row, kv_indptr, kv_indices, heads, kv_heads, dim, vdim, page_size,
-                  scale, sink, splits, tiles_per_split);
+                  scale, sink, splits, tiles_per_split, window, softcap);
     if (splits > 1)
       launch_kernel(sink_merge_kernel<T>, dim3(tokens, heads), dim3(128), 0, (cudaStream_t)stream, (const float*)part, (T*)out, positions, heads,
                     vdim, splits);

@@ -14,7 +14,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 13
+ABI_VERSION = 14
 F32, BF16 = 0, 1
 GATE_FUNCTIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}   # the codes of csrc/roost_kernels.h
 
@@ -118,7 +118,7 @@ _SIGNATURES = {
     "roost_latent_attention_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                   c_int, c_int, c_int, c_float, c_int, c_void_p],
     "roost_mamba2_conv": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                          c_int, c_int, c_int, c_void_p],
+                          c_int, c_int, c_int, c_int, c_void_p],
     "roost_mamba2_conv_state": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "roost_mamba2_scan": [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                           c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
@@ -139,9 +139,21 @@ _SIGNATURES = {
                           c_int, c_void_p],
     "roost_gated_act_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "roost_sink_attention_prepare": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                     c_int, c_float, c_int, c_int, c_void_p],
+                                     c_int, c_float, c_int, c_int, c_int, c_void_p],
     "roost_sink_attention": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                             c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p],
+                             c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "roost_wide_rms_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+    "roost_normed_mean": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+    "roost_pair_embedding": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                             c_int, c_int, c_int, c_void_p],
+    "roost_last_token_store": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "roost_add_bias": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "roost_gelu_mul_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "roost_gated_recurrence_scan": [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                                    c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "roost_matrix_memory_scan": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                                 c_float, c_int, c_void_p],
+    "roost_head_norm_gate": [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "roost_mamba1_scan": [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
     "roost_mamba1_scan_chunks": [c_int, c_int],
@@ -626,12 +638,16 @@ class KernelLibrary:
         return out
 
     # ------------------------------------------------------------------ the Mamba-2 recurrence
-    def mamba2_conv(self, u, col, channels, w, b, state, conv_off, token_row, q_indptr, slots) -> torch.Tensor:
+    def mamba2_conv(self, u, col, channels, w, b, state, conv_off, token_row, q_indptr, slots, activation: str = "silu") -> torch.Tensor:
+        """``activation``: "silu" of the sum, or "none"."""
+        if activation not in ("silu", "none"):
+            raise KernelError(f"mamba2_conv: activation '{activation}' is neither silu nor none")
         _need(u, "u"); _need(w, "w", torch.float32); _need(b, "b", torch.float32); _need(state, "state", torch.float32)
         T = u.shape[0]
         out = torch.empty((T, channels), dtype=u.dtype, device=u.device)
         self._call("roost_mamba2_conv", _ptr(u), u.stride(0), col, _ptr(out), _ptr(w), _ptr(b), _ptr(state), state.stride(0), conv_off,
-                   _ptr(token_row), _ptr(q_indptr), _ptr(slots), T, channels, w.shape[1], dtype_code(u.dtype), _stream())
+                   _ptr(token_row), _ptr(q_indptr), _ptr(slots), T, channels, w.shape[1], 1 if activation == "silu" else 0, dtype_code(u.dtype),
+                   _stream())
         return out
 
     def mamba2_conv_state(self, u, col, channels, taps, state, conv_off, q_indptr, slots) -> None:
@@ -838,8 +854,9 @@ class KernelLibrary:
         return k_pool.data_ptr(), v_pool.data_ptr(), dim
 
     def sink_attention_prepare(self, qkv, k_pool, v_pool, inv_freq, rotary_dim, positions, slot_mapping, heads, kv_heads, dim, vdim, eps,
-                               page_size, q_out: torch.Tensor | None = None) -> None:
-        """``q_out`` [tokens, heads, dim]: where the prepared queries go instead of back into ``qkv``."""
+                               page_size, q_out: torch.Tensor | None = None, halves: bool = False) -> None:
+        """``q_out`` [tokens, heads, dim]: where the prepared queries go instead of back into ``qkv``. ``halves``: element i of the
+        rotated part is paired with element i + rotary_dim / 2 instead of its neighbour."""
         if q_out is not None:
             _need(q_out, "q_out", qkv.dtype)
             if tuple(q_out.shape) != (qkv.shape[0], heads, dim):
@@ -854,7 +871,7 @@ class KernelLibrary:
         kb, vb, entry = self._sink_cache(k_pool, v_pool, dim, vdim)
         self._call("roost_sink_attention_prepare", _ptr(qkv), qkv.stride(0), _ptr(q_out), kb, vb, entry, _ptr(inv_freq) if rotary_dim else None, _ptr(positions),
                    _ptr(slot_mapping), qkv.shape[0], heads, kv_heads, dim, vdim, rotary_dim, float(eps) if eps else 0.0, page_size,
-                   dtype_code(qkv.dtype), _stream())
+                   1 if halves else 0, dtype_code(qkv.dtype), _stream())
 
     def sink_splits_for(self, tokens: int, gy: int, kv_cap: int) -> tuple[int, int]:
         """(blocks a token's key tiles are dealt to, tiles a block): 1 when the step's blocks fill the device by themselves,
@@ -868,8 +885,9 @@ class KernelLibrary:
         return -(-tiles // per), per
 
     def sink_attention(self, qkv, k_pool, v_pool, positions, token_row, kv_indptr, kv_indices, heads, kv_heads, dim, vdim, scale, sink,
-                       kv_cap: int = 0) -> torch.Tensor:
-        """Attention of the step's (prepared) queries over the paged cache in 32-bit arithmetic: out [T, heads * vdim]."""
+                       kv_cap: int = 0, window: int | None = None, softcap: float = 0.0) -> torch.Tensor:
+        """Attention of the step's (prepared) queries over the paged cache in 32-bit arithmetic: out [T, heads * vdim]. ``window``:
+        the keys a query sees, its own included (None: all); ``softcap`` c > 0: a scaled score s becomes c tanh(s / c)."""
         _need(qkv, "qkv"); _need(k_pool, "k_pool", qkv.dtype)
         for n, t in (("positions", positions), ("token_row", token_row), ("kv_indptr", kv_indptr), ("kv_indices", kv_indices)):
             _need(t, n, torch.int32)
@@ -877,11 +895,123 @@ class KernelLibrary:
         kb, vb, entry = self._sink_cache(k_pool, v_pool, dim, vdim)
         out = torch.empty((T, heads * vdim), dtype=qkv.dtype, device=qkv.device)
         gy = kv_heads * (-(-(heads // kv_heads) // 8))
-        splits, per = self.sink_splits_for(T, gy, kv_cap) if kv_cap else (1, 1 << 24)
+        # a window's keys span at most window + 31 positions' worth of tiles, whatever the requests' lengths are
+        span = min(kv_cap, window + 62) if (window and kv_cap) else kv_cap
+        splits, per = self.sink_splits_for(T, gy, span) if span else (1, 1 << 24)
         part = torch.empty((T * heads * splits * (vdim + 2),), dtype=torch.float32, device=qkv.device) if splits > 1 else None
         self._call("roost_sink_attention", _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(part), kb, vb, entry, _ptr(positions), _ptr(token_row),
                    _ptr(kv_indptr), _ptr(kv_indices), T, heads, kv_heads, dim, vdim, k_pool.shape[2], float(scale), 1 if sink else 0, splits, per,
-                   dtype_code(qkv.dtype), _stream(), launches=2 if splits > 1 else 1)
+                   int(window or 0), float(softcap or 0.0), dtype_code(qkv.dtype), _stream(), launches=2 if splits > 1 else 1)
+        return out
+
+    # ------------------------------------------------------------------ a 32-bit stream with root-mean-square norms
+    def wide_rms_norm(self, stream: torch.Tensor, w: torch.Tensor | None, eps: float, out_dtype: torch.dtype, addend: torch.Tensor | None = None,
+                      extra: torch.Tensor | None = None, rows: torch.Tensor | None = None) -> torch.Tensor:
+        """Root-mean-square norm of the float32 ``stream`` plus ``addend`` (activation dtype) plus ``extra`` (float32), the sums
+        formed in 32-bit and written back unless ``rows`` gathers, into ``out_dtype``; without ``w`` the sum itself, rounded."""
+        _need(stream, "stream", torch.float32)
+        H = stream.shape[-1]
+        if w is not None:
+            _need(w, "w", torch.float32)
+            if w.numel() != H:
+                raise KernelError(f"wide_rms_norm: the weight must have {H} elements")
+        if addend is not None:
+            _need(addend, "addend", out_dtype)
+            if addend.shape != stream.shape:
+                raise KernelError("wide_rms_norm: the addend and the stream differ in shape")
+        if extra is not None:
+            _need(extra, "extra", torch.float32)
+            if extra.shape != stream.shape:
+                raise KernelError("wide_rms_norm: the second addend and the stream differ in shape")
+        if rows is not None:
+            _need(rows, "rows", torch.int32)
+        n = stream.numel() // H if rows is None else rows.numel()
+        out = torch.empty((n, H), dtype=out_dtype, device=stream.device)
+        self._call("roost_wide_rms_norm", _ptr(stream), _ptr(addend), _ptr(extra), _ptr(w), _ptr(out), _ptr(rows), n, H, eps, dtype_code(out_dtype),
+                   _stream())
+        return out
+
+    def normed_mean(self, xs: list, ws: list, eps: float) -> torch.Tensor:
+        """The mean of the branches ``xs`` [T, H], each divided by its root mean square over a row and multiplied by its weight."""
+        n = len(xs)
+        if not 1 <= n <= 4 or len(ws) != n:
+            raise KernelError("normed_mean: one to four branches with a weight each")
+        for x, w in zip(xs, ws):
+            _need(x, "x", xs[0].dtype); _need(w, "w", torch.float32)
+            if x.shape != xs[0].shape or w.numel() != x.shape[1]:
+                raise KernelError("normed_mean: the branches and their weights differ in shape")
+        T, H = xs[0].shape
+        out = torch.empty((T, H), dtype=xs[0].dtype, device=xs[0].device)
+        xp = (c_void_p * n)(*[x.data_ptr() for x in xs])
+        wp = (c_void_p * n)(*[w.data_ptr() for w in ws])
+        self._call("roost_normed_mean", xp, wp, n, _ptr(out), T, H, eps, dtype_code(out.dtype), _stream())
+        return out
+
+    def pair_embedding(self, table, pairs, ids, positions, token_row, q_indptr, slots, state, buckets: int, mul_prev: int, mul_cur: int) -> torch.Tensor:
+        """table[ids] + pairs[(previous id * mul_prev + id * mul_cur) mod buckets] as a float32 stream; ``state`` int32 [slots, 1] holds
+        the id before each request's next token."""
+        _need(table, "table"); _need(pairs, "pairs", table.dtype); _need(ids, "ids", torch.int32); _need(state, "state", torch.int32)
+        for n, t in (("positions", positions), ("token_row", token_row), ("q_indptr", q_indptr), ("slots", slots)):
+            _need(t, n, torch.int32)
+        T, (V, H) = ids.numel(), table.shape
+        if tuple(pairs.shape) != (buckets + 1, H):
+            raise KernelError(f"pair_embedding: the pair table must be [{buckets + 1}, {H}]")
+        out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+        self._call("roost_pair_embedding", _ptr(table), _ptr(pairs), _ptr(ids), _ptr(positions), _ptr(token_row), _ptr(q_indptr), _ptr(slots),
+                   _ptr(state), _ptr(out), T, H, V, buckets, mul_prev, mul_cur, dtype_code(table.dtype), _stream())
+        return out
+
+    def last_token_store(self, ids, q_indptr, slots, state) -> None:
+        _need(ids, "ids", torch.int32); _need(state, "state", torch.int32)
+        self._call("roost_last_token_store", _ptr(ids), _ptr(q_indptr), _ptr(slots), _ptr(state), slots.numel(), _stream())
+
+    def add_bias_(self, y: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+        _need(y, "y", torch.float32); _need(bias, "bias", torch.float32)
+        if y.dim() != 2 or bias.numel() != y.shape[1]:
+            raise KernelError("add_bias: one bias a column of a [rows, width] tensor")
+        self._call("roost_add_bias", _ptr(y), _ptr(bias), y.shape[0], y.shape[1], _stream())
+        return y
+
+    def gelu_mul_rows(self, gate: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        """gelu_tanh(gate) * table[ids], the function on the 32-bit values."""
+        _need(gate, "gate"); _need(table, "table", gate.dtype); _need(ids, "ids", torch.int32)
+        T, D = gate.shape
+        if table.shape[1] != D or ids.numel() != T:
+            raise KernelError("gelu_mul_rows: the table's rows and the gate's differ in width")
+        out = torch.empty_like(gate)
+        self._call("roost_gelu_mul_rows", _ptr(gate), _ptr(table), _ptr(ids), _ptr(out), T, D, table.shape[0], dtype_code(gate.dtype), _stream())
+        return out
+
+    # ------------------------------------------------------------------ the gated linear recurrence, the matrix memory
+    def gated_recurrence_scan(self, u, gates, yx, gate_bias, decay, state, q_indptr, slots, width: int, blocks: int) -> torch.Tensor:
+        """S <- a S + sqrt(1 - a^2) i u a channel, out = S gelu_tanh(y): see csrc/gated_recurrence.cu."""
+        _need(u, "u"); _need(gates, "gates", torch.float32); _need(yx, "yx", u.dtype); _need(state, "state", torch.float32)
+        _need(gate_bias, "gate_bias", torch.float32); _need(decay, "decay", torch.float32)
+        T = u.shape[0]
+        if tuple(u.shape) != (T, width) or tuple(gates.shape) != (blocks, T, 2 * (width // blocks)) or gate_bias.numel() != 2 * width or decay.numel() != width:
+            raise KernelError("gated_recurrence_scan: the gates, biases or decays do not fit the sizes")
+        out = torch.empty((T, width), dtype=u.dtype, device=u.device)
+        self._call("roost_gated_recurrence_scan", _ptr(u), _ptr(gates), _ptr(yx), yx.stride(0), _ptr(out), _ptr(gate_bias), _ptr(decay), _ptr(state),
+                   state.stride(0), _ptr(q_indptr), _ptr(slots), slots.numel(), T, width, blocks, dtype_code(u.dtype), _stream())
+        return out
+
+    def matrix_memory_scan(self, qkv, gates, state, q_indptr, slots, heads: int, dim: int, vdim: int, cap: float, floor: float) -> torch.Tensor:
+        """The matrix memory's outputs a head before their norm, float32 [T, heads * vdim]: see csrc/matrix_memory.cu."""
+        _need(qkv, "qkv"); _need(gates, "gates", torch.float32); _need(state, "state", torch.float32)
+        T = qkv.shape[0]
+        if tuple(gates.shape) != (T, 2 * heads) or qkv.shape[1] < heads * (2 * dim + vdim):
+            raise KernelError("matrix_memory_scan: the gates or the projection's rows do not fit the sizes")
+        out = torch.empty((T, heads * vdim), dtype=torch.float32, device=qkv.device)
+        self._call("roost_matrix_memory_scan", _ptr(qkv), qkv.stride(0), _ptr(gates), _ptr(out), _ptr(state), state.stride(0), _ptr(q_indptr),
+                   _ptr(slots), slots.numel(), heads, dim, vdim, float(cap), float(floor), dtype_code(qkv.dtype), _stream())
+        return out
+
+    def head_norm_gate(self, o, u, col: int, w, heads: int, eps: float, out_dtype) -> torch.Tensor:
+        """o / sqrt(mean over a head of o^2 + eps) * w * sigmoid(u[:, col : col + width]) into ``out_dtype``."""
+        _need(o, "o", torch.float32); _need(u, "u", out_dtype); _need(w, "w", torch.float32)
+        T, V = o.shape
+        out = torch.empty((T, V), dtype=out_dtype, device=o.device)
+        self._call("roost_head_norm_gate", _ptr(o), _ptr(u), u.stride(0), col, _ptr(w), _ptr(out), T, heads, V // heads, eps, dtype_code(out_dtype), _stream())
         return out
 
     # ------------------------------------------------------------------ the selective scan
