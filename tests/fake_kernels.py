@@ -420,7 +420,7 @@ class FakeKernels:
         r = torch.sigmoid(arg[:, :, :bw]).permute(1, 0, 2).reshape(T, width)
         i = torch.sigmoid(arg[:, :, bw:]).permute(1, 0, 2).reshape(T, width)
         a = torch.exp(-decay * r)
-        drive = torch.sqrt(1 - a * a) * i * u.float()
+        drive = torch.sqrt(-torch.expm1(-2.0 * decay * r)) * i * u.float()        # 1 - a^2 without cancellation where a is near one
         y = yx[:, :width].float()
         y = 0.5 * y * (1 + torch.tanh(math.sqrt(2 / math.pi) * (y + 0.044715 * y ** 3)))
         for row in range(slots.numel()):

@@ -72,7 +72,9 @@ def pair_rows(tokens, buckets, mul_prev, mul_cur):
 
 
 def embedding(w, cfg, tokens):
-    b = cfg["embedding"]["bigram"]
+    b = (cfg.get("embedding") or {}).get("bigram")
+    if b is None:
+        return w["embed"][torch.as_tensor(tokens)]
     rows = pair_rows(tokens, b["buckets"], b["mul_prev"], b["mul_cur"])
     return w["embed"][torch.as_tensor(tokens)] + w["bigram"][torch.as_tensor(rows)]
 
