@@ -19,6 +19,14 @@ import torch
 F64 = torch.float64
 RGLRU_RATE = 8.0          # log a = -RGLRU_RATE * r * softplus(lam)
 MATRIX_MEMORY_FLOOR = 1e-6  # added to the matrix memory's denominator
+# ``forward(..., rounding=f)`` passes every norm's and projection's output through f: with a rounding to 16 bits it shows at
+# which positions such rounding alone moves the logits far (a dot product next to zero that decides a direction), so that a
+# test of a 16-bit engine can tell an ill-conditioned position from a fault.
+_ROUND = None
+
+
+def _r(z):
+    return z if _ROUND is None else _ROUND(z)
 
 
 # ------------------------------------------------------------------------------------------------ small functions
@@ -95,8 +103,8 @@ def rglru(h, w, p, m):
     """The gated linear recurrence from an empty state. p: the tensors' prefix ('l0.mix.')."""
     T = h.shape[0]
     W, B = m["width"], m["blocks"]
-    y = gelu_tanh(h @ w[p + "y"].T + w[p + "y.b"])
-    u = causal_conv(h @ w[p + "x"].T + w[p + "x.b"], w[p + "conv"], w[p + "conv.b"])
+    y = gelu_tanh(_r(h @ w[p + "y"].T + w[p + "y.b"]))
+    u = _r(causal_conv(_r(h @ w[p + "x"].T + w[p + "x.b"]), w[p + "conv"], w[p + "conv.b"]))
     ub = u.reshape(T, B, W // B)
     r = sigmoid(torch.einsum("boi,tbi->tbo", w[p + "ra"], ub) + w[p + "ra.b"]).reshape(T, W)
     i = sigmoid(torch.einsum("boi,tbi->tbo", w[p + "ri"], ub) + w[p + "ri.b"]).reshape(T, W)
@@ -116,9 +124,9 @@ def window_attention(h, w, p, m, eps, positions=None):
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     positions = list(range(T)) if positions is None else positions
-    q = (h @ w[p + "q"].T + w[p + "q.b"]).reshape(T, H, d)
-    k = (h @ w[p + "k"].T + w[p + "k.b"]).reshape(T, G, d)
-    v = (h @ w[p + "v"].T + w[p + "v.b"]).reshape(T, G, dv)
+    q = _r(h @ w[p + "q"].T + w[p + "q.b"]).reshape(T, H, d)
+    k = _r(h @ w[p + "k"].T + w[p + "k.b"]).reshape(T, G, d)
+    v = _r(h @ w[p + "v"].T + w[p + "v.b"]).reshape(T, G, dv)
     q = unit_rms(rotate_halves(q, positions, m["rot"]["dims"], m["rot"]["base"]), eps)
     k = unit_rms(rotate_halves(k, positions, m["rot"]["dims"], m["rot"]["base"]), eps)
     pos = torch.as_tensor(positions)
@@ -139,9 +147,9 @@ def matrix_memory(h, w, p, m, eps):
     """The matrix memory with exponential gates, token by token from an empty memory."""
     T = h.shape[0]
     H, d, dv, cap = m["heads"], m["dim"], m["vdim"], m["gate_cap"]
-    q = (h @ w[p + "q"].T).reshape(T, H, d) * d ** -0.5
-    k = (h @ w[p + "k"].T).reshape(T, H, d)
-    v = (h @ w[p + "v"].T).reshape(T, H, dv)
+    q = _r(h @ w[p + "q"].T).reshape(T, H, d) * d ** -0.5
+    k = _r(h @ w[p + "k"].T).reshape(T, H, d)
+    v = _r(h @ w[p + "v"].T).reshape(T, H, dv)
     gi = cap * torch.tanh((h @ w[p + "i"].T + w[p + "i.b"]) / cap)                       # [T, H], the logarithm of the input gate
     gf = log_sigmoid(cap * torch.tanh((h @ w[p + "f"].T + w[p + "f.b"]) / cap))         # the logarithm of the forget gate
     S = torch.zeros(H, d, dv, dtype=F64)
@@ -169,7 +177,7 @@ def parallel(h, w, p, m, eps, positions=None):
 
 # ------------------------------------------------------------------------------------------------ feed-forward, token input
 def dense(h, w, p):
-    return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
+    return _r(silu(_r(h @ w[p + "gate"].T)) * _r(h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
 def token_input(x, w, p, tokens, layer, dim, eps):
@@ -193,8 +201,17 @@ def layer_order(cfg):
     return order + [(i, False) for i in range(stop, n)]
 
 
-def forward(cfg, weights, tokens, collect=None):
+def forward(cfg, weights, tokens, collect=None, rounding=None):
     """Logits [T, vocab] of a whole sequence. ``collect``: a list that receives the residual after every layer run."""
+    global _ROUND
+    _ROUND = rounding
+    try:
+        return _forward(cfg, weights, tokens, collect)
+    finally:
+        _ROUND = None
+
+
+def _forward(cfg, weights, tokens, collect):
     w = {k: v.to(F64) if v.is_floating_point() else v for k, v in weights.items()}
     eps = cfg["norm"]["eps"]
     side = cfg.get("token_side")
@@ -204,7 +221,7 @@ def forward(cfg, weights, tokens, collect=None):
         layer, p = cfg["layers"][i], f"l{i}."
         if again:
             x = x + x0
-        hn = rms_norm(x, w[p + "norm1"], eps)
+        hn = _r(rms_norm(x, w[p + "norm1"], eps))
         if layer["type"] == "rglru":
             x = x + rglru(hn, w, p + "mix.", layer["mixer"])
         elif layer["type"] == "parallel":
@@ -212,7 +229,7 @@ def forward(cfg, weights, tokens, collect=None):
         else:
             raise ValueError(layer["type"])
         if layer.get("mlp") is not None:
-            x = x + dense(rms_norm(x, w[p + "norm2"], eps), w, p + "mlp.")
+            x = x + dense(_r(rms_norm(x, w[p + "norm2"], eps)), w, p + "mlp.")
         if side:
             x = x + token_input(x, w, p + "side.", tokens, i, side["dim"], eps)
         if collect is not None:

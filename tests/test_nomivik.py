@@ -76,9 +76,18 @@ class Run:
     def check(self, rid, ids, weights, what, bf16_bounds=(BF16_TOKEN, BF16_RMS), f32_bounds=(F32_TOKEN, F32_RMS)):
         got = torch.cat(self.logits.pop(rid))
         want = P.forward(self.cfg, weights, list(ids[: got.shape[0]]))
-        err, rms = token_error(got, want), H.rms_error(got, want)
-        print(f"MEASURED {what} {self.dtype}: worst position's error {err:.3e}, rms error {rms:.3e}")
         worst, bound = f32_bounds if self.dtype == torch.float32 else bf16_bounds
+        keep = torch.ones(got.shape[0], dtype=torch.bool)
+        if self.dtype != torch.float32:
+            # Positions where rounding every norm's and projection's output to 16 bits moves the plain logits far by itself
+            # (the matrix memory's output keeps only the direction of S^T q, and when one token holds the memory that
+            # direction hangs on the sign of one dot product, which can lie next to zero) are ill-conditioned, not faulty:
+            # they are left out in 16 bits, and the 32-bit run of the same kernels checks them.
+            rounded = P.forward(self.cfg, weights, list(ids[: got.shape[0]]), rounding=lambda z: z.to(torch.bfloat16).double())
+            keep = position_errors(rounded, want) < worst / 3
+            assert int((~keep).sum()) <= max(3, got.shape[0] // 10), f"{what}: the test's model is ill-conditioned at {int((~keep).sum())} positions"
+        err, rms = float(position_errors(got, want)[keep].max()), H.rms_error(got[keep], want[keep])
+        print(f"MEASURED {what} {self.dtype}: worst position's error {err:.3e}, rms error {rms:.3e}, {int((~keep).sum())} positions left out")
         assert err < worst and rms < bound, f"{what}: worst position's error {err}, rms error {rms}"
         return got, want
 
@@ -86,10 +95,14 @@ class Run:
         return all(p.used_count == 0 for p in self.ex.cache.pools)
 
 
-def token_error(got, want) -> float:
-    """The largest error of one position: root mean square of its logits' differences over that of its logits."""
+def position_errors(got, want):
+    """Every position's error: root mean square of its logits' differences over that of its logits."""
     got, want = got.double().cpu(), want.double().cpu()
-    return float(((got - want).pow(2).mean(-1).sqrt() / want.pow(2).mean(-1).sqrt()).max())
+    return (got - want).pow(2).mean(-1).sqrt() / want.pow(2).mean(-1).sqrt()
+
+
+def token_error(got, want) -> float:
+    return float(position_errors(got, want).max())
 
 
 def ids_for(cfg, n, seed):
