@@ -3,7 +3,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers L] [--impl reference]
     python bench.py --sizes 0.6b|8b|32b          the same line at another model's layer sizes
     python bench.py --workload serving --sizes 0.6b [--requests 32] [--budget 512] [--new-tokens 256] [--max-prompt 2048]
-    python bench.py --workload designs [--design vamatar|lafanex]      the other designs' models beside models of equal size
+    python bench.py --workload designs [--design vamatar|lafanex|nomivik]      the other designs' models beside models of equal size
 
 Prints ONE JSON line. ``value`` is decoded tokens per second over K timed decode steps of ``--batch`` requests
 that each hold ``--context`` tokens, timed on the device with CUDA events; ``e2e`` is the same through the
@@ -441,11 +441,93 @@ def lafanex_main(args) -> int:
     return 0
 
 
+# Nomivik models at the same widths, depths and vocabularies, every layer with a dense feed-forward of 3 x width: of every four
+# layers the first holds a windowed attention with a sink beside a matrix memory (values four times as wide as keys, as the
+# memories of this kind are built), the other three a gated linear recurrence as wide as the model behind a convolution of four
+# taps; a hashed pair embedding and a token input of 128 numbers a layer. The Lafanex model beside each is the closest design the
+# engine has (an attention with a sink every fourth layer, scans between, a 32-bit stream) with dense feed-forwards of the same
+# size in every layer.
+def _nomivik_config(width, heads, dim, dense_ff, layers, vocab, window, **_):
+    attention = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
+                 "mask": {"size": window}, "rot": {"base": 1000000.0, "dims": dim // 2}}
+    memory = {"heads": width // 256, "dim": 64, "vdim": 256, "gate_cap": 15.0}
+    out = []
+    for i in range(layers):
+        if i % 4 == 0:
+            out.append({"type": "parallel", "mixer": {"left": attention, "right": memory}, "mlp": {"kind": "dense", "ff": dense_ff}})
+        else:
+            out.append({"type": "rglru", "mixer": {"width": width, "blocks": width // 128, "conv": 4}, "mlp": {"kind": "dense", "ff": dense_ff}})
+    return {"architecture": "Nomivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "token_side": {"dim": 128},
+            "embedding": {"bigram": {"buckets": 1000003, "mul_prev": 1000033, "mul_cur": 31}}, "layers": out}
+
+
+def _lafanex_dense_config(width, heads, dim, dense_ff, layers, vocab, **_):
+    attention = {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                                                "rot": {"base": 1000000.0, "dims": dim}}}
+    scan = {"type": "mamba1", "mixer": {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}}
+    dense = {"kind": "dense", "ff": dense_ff}
+    return {"architecture": "Lafanex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "streams": 4,
+            "layers": [dict(attention if i % 4 == 0 else scan, mlp=dense) for i in range(layers)]}
+
+
+def build_from_config(config_class, cfg: dict, dtype, seed: int = 0):
+    import torch
+
+    from roost_b200.engine.model import Model
+    from roost_b200.kernels import library
+    from roost_b200.parts import Runtime
+    from roost_b200.weights.random_init import random_parameters
+    spec = config_class.from_dict(cfg).to_spec()
+    model = Model(spec, Runtime(dtype, "cuda", library.load()))
+    model.load(random_parameters(spec, seed, torch.device("cuda"), dtype, std=0.02))
+    return model, cfg
+
+
+def nomivik_main(args) -> int:
+    """Prefill and decode throughput of Nomivik models beside Lafanex models with dense feed-forwards (the closest design the
+    engine has: an attention with a sink, recurrences, a 32-bit stream) of equal width, depth and vocabulary, one JSON line."""
+    import torch
+
+    from roost_b200.config.lafanex import LafanexConfig
+    from roost_b200.config.nomivik import NomivikConfig
+    pk, pk_src = peaks()
+    out = {}
+    for name in args.design_sizes.split(","):
+        s = dict(DESIGN_SIZES[name])
+        s["dim"] = 128 if s["width"] >= 2048 else 64
+        s["dense_ff"] = 3 * s["width"]
+        rec = {}
+        for which in ("nomivik", "lafanex"):
+            if which == "nomivik":
+                model, _ = build_from_config(NomivikConfig, _nomivik_config(**s), torch.bfloat16)
+            else:
+                model, _ = build_from_config(LafanexConfig, _lafanex_dense_config(**s), torch.bfloat16)
+            r = {"weight_gb": round(model.weight_bytes() / 1e9, 3)}
+            ms = timed_prefill(model, args.prefill_tokens)
+            r["prefill"] = {"tokens": args.prefill_tokens, "ms": round(ms, 3), "tokens_per_s": round(args.prefill_tokens / ms * 1e3)}
+            for batch in _ints(args.design_batches):
+                tps, ms, launches, _ = timed_decode(model, batch, args.design_context, args.steps, max(args.warmup, 3))
+                r[f"decode_b{batch}"] = {"context": args.design_context, "ms": round(ms, 4), "tokens_per_s": round(tps), "launches": launches[0] // args.steps,
+                                         "library_launches": launches[1] // args.steps}
+            rec[which] = r
+            del model
+            gc.collect()
+            torch.cuda.empty_cache()
+        rec["config"] = {k: s[k] for k in ("width", "heads", "dim", "dense_ff", "layers", "vocab", "window")}
+        out[name] = rec
+    print(json.dumps({"metric": "prefill and decode tokens/s of Nomivik models beside Lafanex models of equal width, depth, vocabulary and feed-forward size",
+                      "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "impl": "ours", "peaks": pk_src,
+                      "data": "synthetic: seeded random weights, seeded random tokens; device-timed with CUDA events", "sizes": out}))
+    return 0
+
+
 def designs_main(args) -> int:
     """Prefill and decode throughput of Vamatar models beside Qwen3-shaped models of equal size, one JSON line."""
     import torch
     if args.design == "lafanex":
         return lafanex_main(args)
+    if args.design == "nomivik":
+        return nomivik_main(args)
     pk, pk_src = peaks()
     out = {}
     for name in args.design_sizes.split(","):
@@ -494,8 +576,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="layers built (default: all the layers of --sizes)")
     ap.add_argument("--sizes", default="8b", choices=sorted(SIZES), help="whose layer sizes: Qwen3-0.6B, -8B (the headline) or -32B")
     ap.add_argument("--design-sizes", default="w1024,w2048", help="--workload designs: which of the Vamatar layer sizes to measure")
-    ap.add_argument("--design", default="vamatar", choices=["vamatar", "lafanex"],
-                    help="--workload designs: vamatar (beside Qwen3-shaped models) or lafanex (beside Vamatar models of equal size)")
+    ap.add_argument("--design", default="vamatar", choices=["vamatar", "lafanex", "nomivik"],
+                    help="--workload designs: vamatar (beside Qwen3-shaped models), lafanex (beside Vamatar models of equal size) or "
+                         "nomivik (beside Lafanex models with dense feed-forwards of equal size)")
     ap.add_argument("--design-batches", default="1,8", help="--workload designs: decode batch sizes")
     ap.add_argument("--design-context", type=int, default=1024, help="--workload designs: keys every decoding request holds")
     ap.add_argument("--workload", default="decode", choices=["decode", "serving", "designs"],

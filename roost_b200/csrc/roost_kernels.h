@@ -411,17 +411,23 @@ int roost_gelu_mul_rows(const void* gate, const void* table, const int32_t* ids,
                         roost_stream_t stream);
 
 /* ---- the gated linear recurrence (gated_recurrence.cu) ---- */
-/* u [tokens, width]; gates float[blocks][tokens][2 * width / blocks]; yx rows [y | ...]; state slots [S: width | ...]. */
+/* u [tokens, width]; gates float[blocks][tokens][2 * width / blocks]; yx rows [y | ...]; state slots [S: width | ...].
+ * ws_state, ws_decay: float[roost_gated_recurrence_scan_chunks(tokens, rows) * width] each, or both null. With them the rows are
+ * cut into chunks of 64 tokens that run side by side (three launches); without, every row is walked in one pass. */
+int roost_gated_recurrence_scan_chunks(int tokens, int rows);
 int roost_gated_recurrence_scan(const void* u, const float* gates, const void* yx, int64_t ld_yx, void* out, const float* gate_bias,
                                 const float* decay, float* state, int64_t state_stride, const int32_t* q_indptr, const int32_t* slots,
-                                int rows, int tokens, int width, int blocks, int dtype, roost_stream_t stream);
+                                int rows, int tokens, int width, int blocks, float* ws_state, float* ws_decay, int dtype, roost_stream_t stream);
 
 /* ---- the matrix memory (matrix_memory.cu) ---- */
 /* qkv rows [q: heads x dim | k: heads x dim | v: heads x vdim | ...]; gates float[tokens][i a head | f a head]; out float[tokens,
  * heads * vdim]; state slots, head after head, [S: dim x vdim | n: dim | m]. */
+/* ws: float[roost_matrix_memory_scan_chunks(tokens, rows) * heads * (dim * vdim + dim + 3)], or null. With it the rows are cut into
+ * chunks of 64 tokens that run side by side (three launches); without, every row is walked in one pass. */
+int roost_matrix_memory_scan_chunks(int tokens, int rows);
 int roost_matrix_memory_scan(const void* qkv, int64_t ld, const float* gates, float* out, float* state, int64_t state_stride,
-                             const int32_t* q_indptr, const int32_t* slots, int rows, int heads, int dim, int vdim, float cap, float floor_,
-                             int dtype, roost_stream_t stream);
+                             const int32_t* q_indptr, const int32_t* slots, int rows, int tokens, int heads, int dim, int vdim, float cap,
+                             float floor_, float* ws, int dtype, roost_stream_t stream);
 /* out = o / sqrt(mean over a head of o^2 + eps) * w * sigmoid(u[:, col:]). */
 int roost_head_norm_gate(const float* o, const void* u, int64_t ld_u, int col, const float* w, void* out, int tokens, int heads, int vdim,
                          float eps, int dtype, roost_stream_t stream);

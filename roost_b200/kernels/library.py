@@ -149,10 +149,12 @@ _SIGNATURES = {
     "roost_last_token_store": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "roost_add_bias": [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "roost_gelu_mul_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "roost_gated_recurrence_scan_chunks": [c_int, c_int],
     "roost_gated_recurrence_scan": [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
-                                    c_int, c_int, c_int, c_int, c_int, c_void_p],
-    "roost_matrix_memory_scan": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
-                                 c_float, c_int, c_void_p],
+                                    c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+    "roost_matrix_memory_scan_chunks": [c_int, c_int],
+    "roost_matrix_memory_scan": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                 c_float, c_float, c_void_p, c_int, c_void_p],
     "roost_head_norm_gate": [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "roost_mamba1_scan": [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
@@ -983,27 +985,41 @@ class KernelLibrary:
         return out
 
     # ------------------------------------------------------------------ the gated linear recurrence, the matrix memory
-    def gated_recurrence_scan(self, u, gates, yx, gate_bias, decay, state, q_indptr, slots, width: int, blocks: int) -> torch.Tensor:
-        """S <- a S + sqrt(1 - a^2) i u a channel, out = S gelu_tanh(y): see csrc/gated_recurrence.cu."""
+    def gated_recurrence_scan(self, u, gates, yx, gate_bias, decay, state, q_indptr, slots, width: int, blocks: int, chunked: bool | None = None) -> torch.Tensor:
+        """S <- a S + sqrt(1 - a^2) i u a channel, out = S gelu_tanh(y): see csrc/gated_recurrence.cu. ``chunked`` None: steps of
+        ``SCAN_CHUNKED_MIN_TOKENS`` tokens or more cut their rows into chunks that run side by side."""
         _need(u, "u"); _need(gates, "gates", torch.float32); _need(yx, "yx", u.dtype); _need(state, "state", torch.float32)
         _need(gate_bias, "gate_bias", torch.float32); _need(decay, "decay", torch.float32)
         T = u.shape[0]
         if tuple(u.shape) != (T, width) or tuple(gates.shape) != (blocks, T, 2 * (width // blocks)) or gate_bias.numel() != 2 * width or decay.numel() != width:
             raise KernelError("gated_recurrence_scan: the gates, biases or decays do not fit the sizes")
         out = torch.empty((T, width), dtype=u.dtype, device=u.device)
+        ws_state = ws_decay = None
+        if (T >= self.SCAN_CHUNKED_MIN_TOKENS) if chunked is None else chunked:
+            chunks = self._lib.roost_gated_recurrence_scan_chunks(T, slots.numel())
+            ws_state = torch.empty((chunks * width,), dtype=torch.float32, device=u.device)
+            ws_decay = torch.empty((chunks * width,), dtype=torch.float32, device=u.device)
         self._call("roost_gated_recurrence_scan", _ptr(u), _ptr(gates), _ptr(yx), yx.stride(0), _ptr(out), _ptr(gate_bias), _ptr(decay), _ptr(state),
-                   state.stride(0), _ptr(q_indptr), _ptr(slots), slots.numel(), T, width, blocks, dtype_code(u.dtype), _stream())
+                   state.stride(0), _ptr(q_indptr), _ptr(slots), slots.numel(), T, width, blocks, _ptr(ws_state), _ptr(ws_decay), dtype_code(u.dtype),
+                   _stream(), launches=3 if ws_state is not None else 1)
         return out
 
-    def matrix_memory_scan(self, qkv, gates, state, q_indptr, slots, heads: int, dim: int, vdim: int, cap: float, floor: float) -> torch.Tensor:
-        """The matrix memory's outputs a head before their norm, float32 [T, heads * vdim]: see csrc/matrix_memory.cu."""
+    def matrix_memory_scan(self, qkv, gates, state, q_indptr, slots, heads: int, dim: int, vdim: int, cap: float, floor: float,
+                           chunked: bool | None = None) -> torch.Tensor:
+        """The matrix memory's outputs a head before their norm, float32 [T, heads * vdim]: see csrc/matrix_memory.cu. ``chunked``
+        None: steps of ``SCAN_CHUNKED_MIN_TOKENS`` tokens or more cut their rows into chunks that run side by side."""
         _need(qkv, "qkv"); _need(gates, "gates", torch.float32); _need(state, "state", torch.float32)
         T = qkv.shape[0]
         if tuple(gates.shape) != (T, 2 * heads) or qkv.shape[1] < heads * (2 * dim + vdim):
             raise KernelError("matrix_memory_scan: the gates or the projection's rows do not fit the sizes")
         out = torch.empty((T, heads * vdim), dtype=torch.float32, device=qkv.device)
+        ws = None
+        if (T >= self.SCAN_CHUNKED_MIN_TOKENS) if chunked is None else chunked:
+            chunks = self._lib.roost_matrix_memory_scan_chunks(T, slots.numel())
+            ws = torch.empty((chunks * heads * (dim * vdim + dim + 3),), dtype=torch.float32, device=qkv.device)
         self._call("roost_matrix_memory_scan", _ptr(qkv), qkv.stride(0), _ptr(gates), _ptr(out), _ptr(state), state.stride(0), _ptr(q_indptr),
-                   _ptr(slots), slots.numel(), heads, dim, vdim, float(cap), float(floor), dtype_code(qkv.dtype), _stream())
+                   _ptr(slots), slots.numel(), T, heads, dim, vdim, float(cap), float(floor), _ptr(ws), dtype_code(qkv.dtype), _stream(),
+                   launches=3 if ws is not None else 1)
         return out
 
     def head_norm_gate(self, o, u, col: int, w, heads: int, eps: float, out_dtype) -> torch.Tensor:
