@@ -458,7 +458,7 @@ def _nomivik_config(width, heads, dim, dense_ff, layers, vocab, window, **_):
         else:
             out.append({"type": "rglru", "mixer": {"width": width, "blocks": width // 128, "conv": 4}, "mlp": {"kind": "dense", "ff": dense_ff}})
     return {"architecture": "Nomivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "token_side": {"dim": 128},
-            "embedding": {"bigram": {"buckets": 1000003, "mul_prev": 1000033, "mul_cur": 31}}, "layers": out}
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000033, "mul_cur": 31}}, "layers": out}
 
 
 def _lafanex_dense_config(width, heads, dim, dense_ff, layers, vocab, **_):

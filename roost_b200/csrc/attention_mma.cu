@@ -241,7 +241,7 @@ struct RowStateM {
 template <int D, int BN, int MT>
 __device__ __forceinline__ void attend_tile_m(RowStateM<D, MT>& st, uint32_t q_smem, int q_row0, uint32_t k_smem, uint32_t v_smem,
                                               int key_row0, int j0, const int (&qpos)[MT][2], const int (&qlo)[MT][2], float scale_log2,
-                                              int lane, bool wide = false) {
+                                              int lane, bool wide = false, float cap_log2 = 0.f) {
   constexpr int NT = BN / 8;
   float s[MT][NT][4];
 #pragma unroll
@@ -266,6 +266,16 @@ __device__ __forceinline__ void attend_tile_m(RowStateM<D, MT>& st, uint32_t q_s
     }
   }
   float corr[MT][2];
+  if (cap_log2 > 0.f) {   // a cap on the scores: s <- c tanh(s / c), here with s and c in log2 units; the scale is then spent
+    const float to_cap = scale_log2 / cap_log2;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[mt][n][e] = cap_log2 * tanhf(s[mt][n][e] * to_cap);
+    scale_log2 = 1.0f;
+  }
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
     float mx[2] = {-INFINITY, -INFINITY};
@@ -393,7 +403,8 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const __nv_bfloa
                                                                 const int32_t* __restrict__ q_indptr, const int32_t* __restrict__ kv_lens,
                                                                 const int32_t* __restrict__ kv_indptr,
                                                                 const int32_t* __restrict__ kv_indices, const int2* __restrict__ work,
-                                                                int q_heads, int kv_heads, int page_size, int page_shift, float scale_log2, int window) {
+                                                                int q_heads, int kv_heads, int page_size, int page_shift, float scale_log2, int window,
+                                                                float cap_log2) {
   const float sink = (window & ROOST_ATTENTION_SINK) ? 1.0f : 0.f;     // one more term, 2^(0 - m), in every row's denominator
   const bool wide = (window & ROOST_ATTENTION_WIDE_WEIGHTS) != 0;       // the weights enter P V as two bfloat16 operands
   window &= ~(ROOST_ATTENTION_SINK | ROOST_ATTENTION_WIDE_WEIGHTS);
@@ -473,7 +484,7 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const __nv_bfloa
     for (int half = 0; half < BN / HALF; ++half) {
       const int j0 = t * BN + half * HALF;
       if (j0 <= warp_hi && j0 + HALF - 1 >= warp_lo) {  // uniform in the warp
-        attend_tile_m<D, HALF, MT>(st, q_smem, warp * 16 * MT, k_smem[stage], v_smem[stage], half * HALF, j0, qpos, qlo, scale_log2, lane, wide);
+        attend_tile_m<D, HALF, MT>(st, q_smem, warp * 16 * MT, k_smem[stage], v_smem[stage], half * HALF, j0, qpos, qlo, scale_log2, lane, wide, cap_log2);
       }
     }
     __syncthreads();
@@ -1252,7 +1263,7 @@ constexpr int kPrefillTwoGroupsMinRows = 49152;
 template <int D, int MT>
 static int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr, const int32_t* kv_lens,
                           const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items, int q_heads, int kv_heads,
-                          int page_size, float scale, int window, cudaStream_t s) {
+                          int page_size, float scale, int window, cudaStream_t s, float softcap = 0.f) {
   const size_t smem = (size_t)(64 * MT + 4 * 64) * D * 2;
   auto kernel = attention_prefill_kernel<D, MT>;
   static bool attr_set = false;  // once per process: nothing but launches happens on later calls (stream capture)
@@ -1262,7 +1273,7 @@ static int launch_prefill(const void* q, void* out, const void* k_pool, const vo
   }
   launch_kernel(kernel, dim3(items, kv_heads), dim3(128), smem, s, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool,
                 (const __nv_bfloat16*)v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, (const int2*)work, q_heads, kv_heads, page_size,
-                page_shift_of(page_size), scale * kLog2e, window);
+                page_shift_of(page_size), scale * kLog2e, window, softcap * kLog2e);
   return check_launch("attention_prefill");
 }
 
@@ -1427,17 +1438,18 @@ extern "C" int roost_attention_mma_supported(int head_dim) {
   return head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256;
 }
 
-extern "C" int roost_attention_prefill(const void* q, long long tokens, void* out, const void* k_pool, const void* v_pool,
-                                       const int32_t* q_indptr, const int32_t* kv_lens, const int32_t* kv_indptr,
-                                       const int32_t* kv_indices, const int32_t* work, int items, int tile_rows, int q_heads, int kv_heads,
-                                       int head_dim, int page_size, long long pool_pages, float scale, int window, roost_stream_t stream) {
+static int attention_prefill(const void* q, long long tokens, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
+                             const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items,
+                             int tile_rows, int q_heads, int kv_heads, int head_dim, int page_size, long long pool_pages, float scale, int window,
+                             float softcap, roost_stream_t stream) {
   ROOST_REQUIRE(items >= 0 && q_heads > 0 && kv_heads > 0 && page_size > 0, "attention_prefill: sizes must be positive");
   ROOST_REQUIRE(tile_rows == 64 || ((tile_rows == 128 || tile_rows == 256) && head_dim <= 128),
                 "attention_prefill: a work item has 64 packed rows, or 128 or 256 up to head size 128");
   ROOST_REQUIRE(q_heads % kv_heads == 0, "attention_prefill: q_heads must be a multiple of kv_heads");
   if (kv_heads > 65535) return fail(ROOST_ERR_UNSUPPORTED, "attention_prefill: more than 65535 key/value heads");
   if (items == 0) return ROOST_OK;
-  if ((tile_rows == 128 || tile_rows == 256) && tokens > 0 && !(window & ROOST_ATTENTION_WIDE_WEIGHTS) &&
+  ROOST_REQUIRE(softcap >= 0.f && (softcap == 0.f || tile_rows != 256), "attention_prefill: a cap on the scores is served by the mma.sync kernels (items of 64 or 128 packed rows)");
+  if ((tile_rows == 128 || tile_rows == 256) && tokens > 0 && !(window & ROOST_ATTENTION_WIDE_WEIGHTS) && softcap == 0.f &&
       prefill_tc_serves(head_dim, q_heads, kv_heads, page_size, pool_pages, k_pool, v_pool, q)) {
     return launch_prefill_tc(q, tokens, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, tile_rows, q_heads, kv_heads,
                              head_dim, page_size, pool_pages, scale, window, (cudaStream_t)stream);
@@ -1445,16 +1457,34 @@ extern "C" int roost_attention_prefill(const void* q, long long tokens, void* ou
   ROOST_REQUIRE(tile_rows != 256 || !(window & ROOST_ATTENTION_WIDE_WEIGHTS), "attention_prefill: work items of 256 packed rows belong to the tcgen05 kernel, which takes no wide weights");
   if (tile_rows == 128) {
     switch (head_dim) {
-      case 16: return launch_prefill<16, 2>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream);
-      case 32: return launch_prefill<32, 2>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream);
-      case 64: return launch_prefill<64, 2>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream);
-      case 128: return launch_prefill<128, 2>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream);
+      case 16: return launch_prefill<16, 2>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream, softcap);
+      case 32: return launch_prefill<32, 2>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream, softcap);
+      case 64: return launch_prefill<64, 2>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream, softcap);
+      case 128: return launch_prefill<128, 2>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream, softcap);
       default: return fail(ROOST_ERR_UNSUPPORTED, "attention_prefill: no tensor-core kernel for this head size");
     }
   }
   ROOST_DISPATCH_HEAD_DIM(head_dim, D, return launch_prefill<D, 1>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items,
-                                                                    q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream));
+                                                                    q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream, softcap));
   return ROOST_OK;
+}
+
+extern "C" int roost_attention_prefill(const void* q, long long tokens, void* out, const void* k_pool, const void* v_pool,
+                                       const int32_t* q_indptr, const int32_t* kv_lens, const int32_t* kv_indptr,
+                                       const int32_t* kv_indices, const int32_t* work, int items, int tile_rows, int q_heads, int kv_heads,
+                                       int head_dim, int page_size, long long pool_pages, float scale, int window, roost_stream_t stream) {
+  return attention_prefill(q, tokens, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, tile_rows, q_heads, kv_heads, head_dim,
+                           page_size, pool_pages, scale, window, 0.f, stream);
+}
+
+// The same with a cap c on the scores: a score s (scaled) becomes c tanh(s / c) before the mask and the softmax. mma.sync kernels only.
+extern "C" int roost_attention_prefill_capped(const void* q, long long tokens, void* out, const void* k_pool, const void* v_pool,
+                                              const int32_t* q_indptr, const int32_t* kv_lens, const int32_t* kv_indptr,
+                                              const int32_t* kv_indices, const int32_t* work, int items, int tile_rows, int q_heads,
+                                              int kv_heads, int head_dim, int page_size, long long pool_pages, float scale, int window,
+                                              float softcap, roost_stream_t stream) {
+  return attention_prefill(q, tokens, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, tile_rows, q_heads, kv_heads, head_dim,
+                           page_size, pool_pages, scale, window, softcap, stream);
 }
 
 extern "C" int roost_attention_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,

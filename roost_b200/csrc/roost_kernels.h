@@ -133,6 +133,12 @@ int roost_attention_prefill(const void* q, long long tokens, void* out, const vo
                             const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work,
                             int items, int tile_rows, int q_heads, int kv_heads, int head_dim, int page_size, long long pool_pages,
                             float scale, int window, roost_stream_t stream);
+/* The same with a cap c on the scores: a scaled score s becomes c tanh(s / c) before the mask and the softmax. Served by the mma.sync
+ * kernels: items of 64 or 128 packed rows (roost_attention_prefill_tile_rows_mma). */
+int roost_attention_prefill_capped(const void* q, long long tokens, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
+                            const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work,
+                            int items, int tile_rows, int q_heads, int kv_heads, int head_dim, int page_size, long long pool_pages,
+                            float scale, int window, float softcap, roost_stream_t stream);
 int roost_attention_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
                            const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work,
                            int items, const int32_t* merge_work, int merge_items, int merge_rows, float* part_o, float* part_ml,

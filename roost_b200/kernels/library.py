@@ -75,6 +75,8 @@ _SIGNATURES = {
     "roost_attention_prefill_tile_rows_mma": [c_int, c_int, ctypes.c_longlong],
     "roost_attention_prefill": [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_int, c_int, c_int, ctypes.c_longlong, c_float, c_int, c_void_p],
+    "roost_attention_prefill_capped": [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_int, c_int, c_int, c_int, c_int, c_int, ctypes.c_longlong, c_float, c_int, c_float, c_void_p],
     "roost_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, ctypes.c_longlong, c_float, c_int,
                                c_void_p],
@@ -385,15 +387,18 @@ class KernelLibrary:
         self._lib.roost_attention_set_prefill_tc(1 if on else 0)
 
     attention_mma_sink = True    # the tensor-core kernels take a softmax with one added to its denominator (``sink``)
+    attention_mma_softcap = True  # ... and their prompt kernels a cap on the scores (``softcap``)
     ATTENTION_SINK = 1 << 30     # ROOST_ATTENTION_SINK of csrc/roost_kernels.h
     ATTENTION_WIDE_WEIGHTS = 1 << 29
 
     def attention_mma(self, q, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, plan, scale: float,
-                      window: int | None, sink: bool = False, wide_weights: bool = False) -> torch.Tensor:
+                      window: int | None, sink: bool = False, wide_weights: bool = False, softcap: float = 0.0) -> torch.Tensor:
         """Tensor-core attention (bfloat16). ``plan``: an ``AttentionPlan`` whose work lists are on the device. ``sink``: one is
         added to the softmax's denominator (a key of score 0 that has no value). ``wide_weights``: the softmax weights enter P V as two
         bfloat16 operands (16 bits of the 32-bit weights); the plan's prefill items must then come from
-        ``attention_prefill_tile_rows(..., tensor_memory=False)``."""
+        ``attention_prefill_tile_rows(..., tensor_memory=False)``. ``softcap`` c > 0: a scaled score s becomes c tanh(s / c); the
+        prompt kernels on mma.sync serve it (items from ``tensor_memory=False``), the decode kernels do not: the plan must hold no
+        decode items then."""
         _need(q, "q", torch.bfloat16); _need(k_pool, "k_pool", torch.bfloat16); _need(v_pool, "v_pool", torch.bfloat16)
         T, nq, d = q.shape
         _, nkv, page, d2 = k_pool.shape
@@ -401,7 +406,13 @@ class KernelLibrary:
             raise KernelError("attention_mma: head_dim of q and of the pool differ")
         out = torch.empty((T, nq * d), dtype=q.dtype, device=q.device)
         w = (int(window) if window else 0) | (self.ATTENTION_SINK if sink else 0) | (self.ATTENTION_WIDE_WEIGHTS if wide_weights else 0)
-        if plan.prefill_items:
+        if softcap and plan.decode_items:
+            raise KernelError("attention_mma: the decode kernels know no cap on the scores")
+        if plan.prefill_items and softcap:
+            self._call("roost_attention_prefill_capped", _ptr(q), T, _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(q_indptr), _ptr(kv_lens),
+                       _ptr(kv_indptr), _ptr(kv_indices), _ptr(plan.prefill_work), plan.prefill_items, plan.prefill_tile_rows, nq, nkv, d, page,
+                       k_pool.shape[0], scale, w, float(softcap), _stream())
+        elif plan.prefill_items:
             self._call("roost_attention_prefill", _ptr(q), T, _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(q_indptr), _ptr(kv_lens),
                        _ptr(kv_indptr), _ptr(kv_indices), _ptr(plan.prefill_work), plan.prefill_items, plan.prefill_tile_rows, nq, nkv, d, page,
                        k_pool.shape[0], scale, w, _stream())

@@ -83,8 +83,12 @@ class SinkAttention(Mixer):
         tables = batch.groups[cache.group]
         inv_freq, rotary_dim = self.position.rotation() if self.position is not None else (None, 0)
         qkv = self.qkv(x)
-        # the tensor-core kernels rotate nothing themselves and know no cap on the scores: a capped model runs the 32-bit kernel
-        tensor_cores = (self.two_planes and qkv.dtype == torch.bfloat16 and not s.softcap and getattr(k, "attention_mma_sink", False)
+        # Of the tensor-core kernels only the prompt kernels know a cap on the scores: a capped model runs them in steps all of whose
+        # rows are prompt portions (no row of SHORT_ROW_TOKENS tokens or fewer: the step's class, so a captured step keeps its way),
+        # and the 32-bit kernel in steps that decode.
+        capped_ok = not s.softcap or (getattr(k, "attention_mma_softcap", False) and batch.row_counts
+                                      and not any(n <= SHORT_ROW_TOKENS for n in batch.row_counts))
+        tensor_cores = (self.two_planes and qkv.dtype == torch.bfloat16 and capped_ok and getattr(k, "attention_mma_sink", False)
                         and getattr(k, "attention_mma_supported", lambda d: False)(s.head_dim))
         q = torch.empty((qkv.shape[0], s.num_heads, s.head_dim), dtype=qkv.dtype, device=qkv.device) if tensor_cores else None
         k.sink_attention_prepare(qkv, cache.k_pool, cache.v_pool, inv_freq, rotary_dim, batch.positions, tables.slot_mapping, s.num_heads,
@@ -107,7 +111,7 @@ class SinkAttention(Mixer):
         chunk, cluster = split_for(batch.num_rows, batch.kv_cap, cache.k_pool, cache.v_pool) if split_for and batch.kv_cap else (k.decode_chunk, 0)
         plan = batch.step_work(self, ("sink_attention", group, s.window, chunk, tile_rows, cluster))
         return k.attention_mma(q, cache.k_pool, cache.v_pool, batch.q_indptr, batch.kv_lens, tables.kv_indptr, tables.kv_indices, plan,
-                               s.scale, s.window, sink=s.sink, wide_weights=True)
+                               s.scale, s.window, sink=s.sink, wide_weights=True, **({"softcap": s.softcap} if s.softcap else {}))
 
     def step_class(self, row_counts):
         return ("short_rows", any(n <= SHORT_ROW_TOKENS for n in row_counts))
