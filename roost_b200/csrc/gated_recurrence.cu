@@ -16,9 +16,9 @@ __device__ __forceinline__ float recurrence_exp(float x) { return expf(x); }
 template <>
 __device__ __forceinline__ float recurrence_exp<float>(float x) { return exp_nearest(x); }
 
-constexpr int kGrChunkTokens = 64;
+constexpr int kGrChunkTokens = 16;   // a thread a channel: short chunks give the device enough threads (2,048 tokens x 1,024 channels: 131 k)
 
-// Which (row, chunk) the block `b` of a chunked launch takes: rows in order, each with ceil(tokens / 64) chunks. False beyond
+// Which (row, chunk) the block `b` of a chunked launch takes: rows in order, each with ceil(tokens / 16) chunks. False beyond
 // the step's chunks.
 __device__ __forceinline__ bool recurrence_chunk_of_block(const int32_t* __restrict__ q_indptr, int rows, int b, int& r, int& k, int& chunks_of_row) {
   for (r = 0; r < rows; ++r) {
@@ -103,12 +103,22 @@ __global__ void gated_recurrence_carry_kernel(const float* state, int64_t state_
   const int chunks = (q_indptr[r + 1] - q_indptr[r] + kGrChunkTokens - 1) / kGrChunkTokens;
   if (chunks == 0) return;
   float S = state[(size_t)slots[r] * state_stride + c];
-#pragma unroll 4      // the chunks' own states and decays do not depend on S: several loads in flight
-  for (int k = 0; k < chunks; ++k) {
-    float* w = ws_state + (size_t)(first + k) * width + c;
-    const float own = k < chunks - 1 ? *w : 0.f;
-    *w = S;                                                                  // what chunk k starts from
-    if (k < chunks - 1) S = fmaf(recurrence_exp<T>(-ws_decay[(size_t)(first + k) * width + c]), S, own);
+  constexpr int kBatch = 16;      // the chunks' own states and decays do not depend on S: a batch of loads in flight, then the chain
+  for (int k0 = 0; k0 < chunks; k0 += kBatch) {
+    float own[kBatch], dec[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const bool has = k0 + j < chunks - 1;
+      own[j] = has ? ws_state[(size_t)(first + k0 + j) * width + c] : 0.f;
+      dec[j] = has ? ws_decay[(size_t)(first + k0 + j) * width + c] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      if (k0 + j < chunks) {
+        ws_state[(size_t)(first + k0 + j) * width + c] = S;                  // what chunk k0 + j starts from
+        if (k0 + j < chunks - 1) S = fmaf(recurrence_exp<T>(-dec[j]), S, own[j]);
+      }
+    }
   }
 }
 
@@ -119,7 +129,7 @@ using namespace roost;
 extern "C" int roost_gated_recurrence_scan_chunks(int tokens, int rows) { return (tokens + kGrChunkTokens - 1) / kGrChunkTokens + rows; }
 
 // ws_state and ws_decay (float[chunks * width] each, chunks = roost_gated_recurrence_scan_chunks(tokens, rows)): rows are cut into
-// chunks that run side by side (three launches); null: every row is walked in one pass.
+// chunks of 16 tokens that run side by side (three launches); null: every row is walked in one pass.
 extern "C" int roost_gated_recurrence_scan(const void* u, const float* gates, const void* yx, int64_t ld_yx, void* out, const float* gate_bias,
                                            const float* decay, float* state, int64_t state_stride, const int32_t* q_indptr,
                                            const int32_t* slots, int rows, int tokens, int width, int blocks, float* ws_state, float* ws_decay,

@@ -199,16 +199,31 @@ __global__ void matrix_memory_carry_kernel(const float* state, int64_t state_str
   if (chunks == 0) return;
   const float* slot = state + (size_t)slots[r] * state_stride + (size_t)h * ((size_t)entries + 1);
   float e = slot[idx], m = slot[entries];
-  for (int k = 0; k < chunks; ++k) {
-    float* w = ws + ((size_t)(first + k) * heads + h) * memory_ws_head(dim, vdim);
-    const float own = k < chunks - 1 ? w[idx] : 0.f;
-    w[idx] = e;                                                              // what chunk k starts from
-    if (idx == 0) w[entries + 2] = m;
-    if (k < chunks - 1) {
-      const float m_own = w[entries], f = w[entries + 1];
-      const float m_new = fmaxf(f + m, m_own);
-      e = fmaf(memory_exp<T>(f + m - m_new), e, memory_exp<T>(m_own - m_new) * own);
-      m = m_new;
+  constexpr int kBatch = 8;       // the chunks' own entries, maxima and sums do not depend on e: a batch of loads in flight, then the chain
+  const size_t stride = (size_t)heads * memory_ws_head(dim, vdim);
+  float* w0 = ws + ((size_t)first * heads + h) * memory_ws_head(dim, vdim);
+  for (int k0 = 0; k0 < chunks; k0 += kBatch) {
+    float own[kBatch], m_own[kBatch], f[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const bool has = k0 + j < chunks - 1;
+      const float* w = w0 + (size_t)(k0 + j) * stride;
+      own[j] = has ? w[idx] : 0.f;
+      m_own[j] = has ? w[entries] : 0.f;
+      f[j] = has ? w[entries + 1] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      if (k0 + j < chunks) {
+        float* w = w0 + (size_t)(k0 + j) * stride;
+        w[idx] = e;                                                          // what chunk k0 + j starts from
+        if (idx == 0) w[entries + 2] = m;
+        if (k0 + j < chunks - 1) {
+          const float m_new = fmaxf(f[j] + m, m_own[j]);
+          e = fmaf(memory_exp<T>(f[j] + m - m_new), e, memory_exp<T>(m_own[j] - m_new) * own[j]);
+          m = m_new;
+        }
+      }
     }
   }
 }

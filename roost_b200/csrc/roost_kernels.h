@@ -419,7 +419,7 @@ int roost_gelu_mul_rows(const void* gate, const void* table, const int32_t* ids,
 /* ---- the gated linear recurrence (gated_recurrence.cu) ---- */
 /* u [tokens, width]; gates float[blocks][tokens][2 * width / blocks]; yx rows [y | ...]; state slots [S: width | ...].
  * ws_state, ws_decay: float[roost_gated_recurrence_scan_chunks(tokens, rows) * width] each, or both null. With them the rows are
- * cut into chunks of 64 tokens that run side by side (three launches); without, every row is walked in one pass. */
+ * cut into chunks of 16 tokens that run side by side (three launches); without, every row is walked in one pass. */
 int roost_gated_recurrence_scan_chunks(int tokens, int rows);
 int roost_gated_recurrence_scan(const void* u, const float* gates, const void* yx, int64_t ld_yx, void* out, const float* gate_bias,
                                 const float* decay, float* state, int64_t state_stride, const int32_t* q_indptr, const int32_t* slots,
