@@ -548,3 +548,59 @@ def test_the_random_weights_mode_writes_a_folder_the_engine_runs(tmp_path):
     ex = StepExecutor(model, page_size=4, num_pages=16, max_requests=2)
     out = ex.step([StepEntry("a", [1, 2, 3], [2])])
     assert out.shape == (1, NM.LOOPED["vocab"]) and bool(torch.isfinite(out).all())
+
+
+# ------------------------------------------------------------------------------------------------ the programs a user runs
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_replay_program_on_a_nomivik_model(tmp_path_factory, tmp_path, dtype):
+    """bin/trace_run as a subprocess: the model class found by config.json, three requests through a pool of 192 tokens (the third
+    takes the pages and the slot the first gave back), portions beside single tokens, a request that sits out a step."""
+    from tests.test_trace_run_gpu import TraceRun
+    folder, cfg, weights = model_dir(tmp_path_factory, "mixed", NM.MIXED, seed=5)
+    a, b, c = ids_for(cfg, 70, 21), ids_for(cfg, 45, 22), ids_for(cfg, 100, 23)
+    want = {k: P.forward(cfg, weights, ids) for k, ids in (("a", a), ("b", b), ("c", c))}
+    run = TraceRun(folder, dtype, tmp_path, max_tokens=192)
+    try:
+        got_a = [run.step([("a", a[:38], list(range(38)))])]
+        out = run.step([("b", b[:2], [0, 1]), ("a", a[38:40], [0, 1])])
+        got_b = [out[:2]]
+        got_a.append(out[2:])
+        assert run.step([("b", b[2:30], [])]) is None
+        out = run.step([("a", a[40:41], [0]), ("b", b[30:45], list(range(15)))], end=["b"])
+        got_a.append(out[:1])
+        got_b.append(out[1:])
+        for i in range(41, 70):
+            got_a.append(run.step([("a", a[i : i + 1], [0])], end=["a"] if i == 69 else []))
+        got_c = run.step([("c", c, list(range(100)))], end=["c"])
+    finally:
+        run.close()
+    bound = F32_TOKEN if dtype == "float32" else BF16_TOKEN
+    for what, got, ref in (("a", torch.cat(got_a), want["a"]), ("b, first two", got_b[0], want["b"][:2]), ("b, last portion", got_b[1], want["b"][30:]),
+                           ("c", got_c, want["c"])):
+        errs = position_errors(got, ref)
+        over = int((errs > bound).sum())
+        print(f"MEASURED replay {what} {dtype}: worst position's error {float(errs.max()):.3e}")
+        assert over <= (0 if dtype == "float32" else max(1, len(errs) // 10)), (what, float(errs.max()))
+
+
+@pytest.mark.gpu
+def test_the_command_line_generates_from_a_nomivik_model(tmp_path_factory):
+    import json
+    import subprocess
+    import sys
+
+    from tests.conftest import ROOT
+    folder, cfg, weights = model_dir(tmp_path_factory, "looped", NM.LOOPED, seed=len("looped"))
+    prompt = ids_for(cfg, 12, 3)
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "roost"), "generate", "--model", str(folder), "--dtype", "float32", "--prompt-ids",
+                        ",".join(map(str, prompt)), "--max-output-tokens", "8", "--ignore-eos", "--attention-blocks", "8", "--max-sequences", "2"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    assert out["finish_reason"] == "length" and out["prompt_tokens"] == 12 and len(out["token_ids"]) == 8
+    logits = P.forward(cfg, weights, list(prompt) + out["token_ids"][:-1])
+    for j, tok in enumerate(out["token_ids"]):
+        top = logits[len(prompt) - 1 + j].topk(2)
+        if float(top.values[0] - top.values[1]) > 1e-3:
+            assert tok == int(top.indices[0]), (j, tok, int(top.indices[0]))
