@@ -26,8 +26,8 @@ class MatrixMemory(Mixer):
         s = spec
         if min(s.hidden, s.num_heads, s.head_dim, s.v_dim) <= 0 or not s.gate_cap > 0 or not s.eps > 0 or s.floor < 0:
             raise ValueError("matrix_memory: every size, the gates' cap and eps must be positive")
-        if s.head_dim > 256 or s.v_dim > 1023:
-            raise ValueError(f"matrix_memory: heads of {s.head_dim} keys and {s.v_dim} values; the kernel keeps up to 256 and 1023")
+        if s.head_dim > 1024 or s.v_dim > 65535 * 32:
+            raise ValueError(f"matrix_memory: heads of {s.head_dim} keys and {s.v_dim} values; the kernel keeps up to 1,024 keys a head")
         self.spec, self.rt = s, runtime
         self.qk_width, self.v_width = s.num_heads * s.head_dim, s.num_heads * s.v_dim
         self.head_state = s.head_dim * s.v_dim + s.head_dim + 1

@@ -61,7 +61,7 @@ def test_the_gated_recurrence_walked_and_in_chunks(kernels, dtype, width, blocks
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,dim,vdim", [(2, 20, 36), (1, 64, 70), (3, 100, 32), (1, 160, 40)])
+@pytest.mark.parametrize("heads,dim,vdim", [(2, 20, 36), (1, 64, 70), (3, 100, 32), (1, 160, 40), (1, 520, 33)])
 @pytest.mark.parametrize("chunked", [False, True])
 def test_the_matrix_memory_walked_and_in_chunks(kernels, dtype, heads, dim, vdim, chunked):
     g = torch.Generator().manual_seed(heads * dim + vdim)
