@@ -98,6 +98,45 @@ __global__ void normed_mean_kernel(NormedMeanArgs a, int n, T* __restrict__ out,
   pdl_wait();
   const size_t t = blockIdx.x;
   float inv[4];
+  if constexpr (sizeof(T) == 2) {
+    // rows of 16-bit numbers that the block covers with eight a thread: every branch's row is read once, 16 bytes a thread, and kept
+    bool aligned = reinterpret_cast<uintptr_t>(out) % 16 == 0;
+    for (int b = 0; b < n; ++b) aligned = aligned && reinterpret_cast<uintptr_t>(a.x[b]) % 16 == 0;
+    if (aligned && hidden % 8 == 0 && hidden <= (int)blockDim.x * 8) {
+      const int i8 = threadIdx.x * 8;
+      const bool live = i8 < hidden;
+      float v[4][8];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        if (b < n) {
+          union { uint4 u; T e[8]; } raw;
+          raw.u = live ? *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.x[b]) + t * hidden + i8) : make_uint4(0, 0, 0, 0);
+          float ss = 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            v[b][j] = to_float(raw.e[j]);
+            ss = fmaf(v[b][j], v[b][j], ss);
+          }
+          ss = block_sum(ss, scratch);
+          inv[b] = 1.0f / sqrtf(ss / (float)hidden + eps);
+        }
+      }
+      if (live) {
+        const float share = 1.0f / (float)n;
+        union { uint4 u; T e[8]; } res;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float s = 0.f;
+#pragma unroll
+          for (int b = 0; b < 4; ++b)
+            if (b < n) s = fmaf(v[b][j] * inv[b], a.w[b][i8 + j], s);
+          res.e[j] = from_float<T>(s * share);
+        }
+        *reinterpret_cast<uint4*>(out + t * hidden + i8) = res.u;
+      }
+      return;
+    }
+  }
   for (int b = 0; b < n; ++b) {
     const T* x = reinterpret_cast<const T*>(a.x[b]) + t * hidden;
     float ss = 0.f;
