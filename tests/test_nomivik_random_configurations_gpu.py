@@ -31,9 +31,9 @@ def draw_config(seed: int) -> dict:
             rot = rng.choice([r for r in (2, 4, 6, 8, 16, 32, 64, 128) if r <= dim])
             left = NM.attention(heads=kv_heads * rng.choice([1, 2, 3, 4, 8]), kv_heads=kv_heads, dim=dim, vdim=vdim, rot=rot,
                                 base=rng.choice([50.0, 10000.0, 1000000.0]), scale=rng.choice([0.05, 0.125, 0.3]) * (16.0 / dim) ** 0.5 * 4.0,
-                                window=rng.choice([1, 2, 5, 16, 31, 64, 65, 100, 136, 1000]), softcap=rng.choice([0.5, 5.0, 20.0, 50.0]))
+                                window=rng.choice([1, 2, 5, 16, 31, 64, 65, 100, 150, 1000]), softcap=rng.choice([0.5, 5.0, 15.0, 50.0]))
             right = NM.memory(heads=rng.choice([1, 2, 3, 4, 6]), dim=rng.choice([3, 8, 16, 32, 48, 64, 100, 130]), vdim=rng.choice([5, 8, 31, 32, 33, 64, 100]),
-                              gate_cap=rng.choice([1.0, 6.0, 12.0, 30.0]))
+                              gate_cap=rng.choice([1.0, 6.0, 10.0, 30.0]))
             layer = NM.parallel(left, right)
         else:
             blocks = rng.choice([1, 2, 3, 4, 8])
@@ -43,7 +43,7 @@ def draw_config(seed: int) -> dict:
     if rng.random() < 0.6:
         a = rng.randrange(len(layers))
         loop = (a, rng.randint(a + 1, len(layers)), rng.randint(1, 3))
-    pairs = None if rng.random() < 0.15 else (rng.choice([1, 7, 509, 4099]), rng.choice([0, 1, 127, 1000003]), rng.choice([1, 7, 31, 999983]))
+    pairs = None if rng.random() < 0.15 else (rng.choice([1, 11, 521, 4099]), rng.choice([0, 1, 131, 1000003]), rng.choice([1, 5, 31, 999983]))
     return NM.config(layers, width=width, vocab=rng.randint(50, 700), eps=rng.choice([1e-5, 1e-6]), pairs=pairs,
                      side=rng.choice([None, 1, 2, 8, 24, 40]), loop=loop)
 
