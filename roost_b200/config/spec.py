@@ -62,7 +62,9 @@ class LatentAttentionSpec(MixerSpec):
     that all heads share. A head's key is [W_uk c | shared part] against a query of ``nope_dim`` plain and ``rope_dim``
     rotated numbers, its value W_uv c of ``v_dim`` numbers. ``window`` counts the keys a query sees, its own included
     (None: all). ``own_latent`` False: the run makes no latent and reads another run's; ``cache_window`` is then the
-    window the shared cache is kept for (the widest of the runs that read it; None: everything is kept)."""
+    window the shared cache is kept for (the widest of the runs that read it; None: everything is kept). ``rope_dim`` 0 (and no
+    ``position``): keys have no rotated part and the cache entry is the latent alone. ``head_gate``: head h's output is multiplied
+    by sigmoid((W_g x)_h), one number a token and head, from the mixer's own input."""
     kind: str = "latent_attention"
     hidden: int = 0
     num_heads: int = 0
@@ -76,6 +78,7 @@ class LatentAttentionSpec(MixerSpec):
     own_latent: bool = True
     latent_eps: float = 1e-6
     position: PositionSpec | None = None
+    head_gate: bool = False
 
 
 @dataclass(frozen=True)
@@ -168,6 +171,46 @@ class MatrixMemorySpec(MixerSpec):
 
 
 @dataclass(frozen=True)
+class RetentionSpec(MixerSpec):
+    """Linear attention with a fixed decay a head, no softmax and no denominator. q = W_q h, k = W_k h (``num_heads`` x ``head_dim``),
+    v = W_v h (``num_heads`` x ``v_dim``); q and k are rotated (``position``), k then multiplied by head_dim^(-1/2); per head
+    S <- decay_h S + k v^T from S = 0, o = S^T q. Each head's o is divided by its root mean square (``eps``, no weight); the heads side
+    by side are multiplied by silu(W_g h) and projected out. S is kept per request in 32-bit."""
+    kind: str = "retention"
+    hidden: int = 0
+    num_heads: int = 0
+    head_dim: int = 0
+    v_dim: int = 0
+    decay: tuple = ()
+    eps: float = 1e-6
+    position: PositionSpec | None = None
+
+
+@dataclass(frozen=True)
+class SigmoidAttentionSpec(MixerSpec):
+    """Grouped-query causal attention without a softmax: a visible key j gets the weight sigmoid(s_ij + b_h) of its own, and the
+    weights are not normalized over the keys. Queries and keys are divided by their root mean square over the head (``qk_norm_eps``)
+    and multiplied by a weight of ``head_dim`` numbers shared by the heads (one for queries, one for keys). ``temp_coef`` c > 0: the
+    query at position p is multiplied by 1 + c ln(floor((p + 1) / ``temp_every``) + 1). s_ij = (q_i . k_j) ``scale`` - slope_h (i - j)
+    with one ``slopes`` entry a query head (empty: no distance bias); b_h is a stored number a head (``head_bias``). With
+    ``output_gate`` the heads side by side are multiplied element by element by sigmoid(W_g h) before the output projection. No
+    position encoding. The cache keeps one entry [key | value] a token and key/value head, or two planes when their sizes agree."""
+    kind: str = "sigmoid_attention"
+    hidden: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    v_dim: int = 0
+    scale: float = 0.0
+    qk_norm_eps: float = 1e-6
+    temp_coef: float = 0.0
+    temp_every: int = 1
+    slopes: tuple = ()
+    head_bias: bool = True
+    output_gate: bool = True
+
+
+@dataclass(frozen=True)
 class ParallelMixerSpec(MixerSpec):
     """Several mixers side by side that read the same input; the result is the mean of their outputs, each first divided by
     its root mean square over the model width (``eps``) and multiplied by a weight of its own. Every branch keeps the cache
@@ -193,6 +236,16 @@ class GatedMlpSpec(FeedForwardSpec):
     intermediate: int = 0
     activation: str = "silu"
     limit: float = 0.0
+
+
+@dataclass(frozen=True)
+class DenseMlpSpec(FeedForwardSpec):
+    """down(act(x Wu^T)), no gate. ``activation`` "xielu": with two stored numbers (p, q), act(z) = softplus(p) z^2 + z / 2 for
+    z > 0 and (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 for z <= 0."""
+    kind: str = "dense_mlp"
+    hidden: int = 0
+    intermediate: int = 0
+    activation: str = "xielu"
 
 
 @dataclass(frozen=True)
@@ -257,6 +310,13 @@ class CappedHeadSpec(HeadSpec):
 
 
 @dataclass(frozen=True)
+class ScaledHeadSpec(HeadSpec):
+    """logits = (final W^T) * scale in 32-bit."""
+    kind: str = "scaled_linear"
+    scale: float = 1.0
+
+
+@dataclass(frozen=True)
 class PairHashedEmbeddingSpec(EmbeddingSpec):
     """h0[t] = table[id_t] + pairs[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets] as a 32-bit stream; a request's first
     token takes row ``buckets`` of ``pairs`` (the row after the buckets). The previous token is kept per request."""
@@ -292,11 +352,20 @@ class ConnectionSpec:
 
 
 @dataclass(frozen=True)
+class GatedResidualSpec(ConnectionSpec):
+    """A sublayer's output y is multiplied element by element by sigmoid(W h + b) before it is added to the residual, h being the
+    sublayer's own (normed) input and W a square matrix of the model's width: x <- x + y sigmoid(W h + b)."""
+    kind: str = "sigmoid_gate"
+    hidden: int = 0
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer's parts and their arrangement. ``pre_norm``: h += mixer(norm1(h)); h += ff(norm2(h)), the stream in the
     activation dtype. ``pre_norm_wide``: the same with the stream kept and summed in 32-bit whatever the activation dtype
     is; its ``feed_forward`` and ``post_mixer_norm`` may be None (a layer that is its mixer only). ``pre_norm_streams``:
-    the same two sublayers over several 32-bit residual streams, read and written through ``connection``."""
+    the same two sublayers over several 32-bit residual streams, read and written through ``connection``. ``pre_norm_gated``:
+    ``pre_norm_wide`` with every sublayer's output scaled by a gate of its ``connection`` (``sigmoid_gate``) before the sum."""
     mixer: MixerSpec
     feed_forward: FeedForwardSpec | None
     input_norm: NormSpec

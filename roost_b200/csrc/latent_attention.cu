@@ -6,7 +6,7 @@
 // latent_prepare: per token, the latent divided by its root mean square (eps inside the root) times a weight, the shared key
 // part rotated, both written to the token's cache slot; every head's rotated query part rotated in place. The rotation pairs
 // element i with i + dims/2 of the part's first `dims` elements; the angle position * inv_freq[i] is formed in 64-bit and
-// reduced to [-pi, pi] before the 32-bit sincosf.
+// reduced to [-pi, pi] before the 32-bit sincosf. rope 0: keys have no rotated part and the entry is the latent alone.
 //
 // latent_attention: one block per (query token, 8 heads, split); a warp a head. Keys are visited in tiles of 32 at absolute
 // positions that are multiples of 32, a lane a key for the scores, a lane a latent dimension for the sums; the tile is read
@@ -203,9 +203,9 @@ using namespace roost;
 extern "C" int roost_latent_prepare(void* q, const void* down, void* pool, const float* latent_w, const double* inv_freq,
                                     const int32_t* positions, const int32_t* slot_mapping, int tokens, int heads, int nope, int rope,
                                     int rot_dims, int rank, float eps, int dtype, roost_stream_t stream) {
-  ROOST_REQUIRE(tokens >= 0 && heads > 0 && nope > 0 && rope > 0 && rank > 0, "latent_prepare: sizes must be positive");
-  ROOST_REQUIRE(rot_dims > 0 && rot_dims % 2 == 0 && rot_dims <= rope, "latent_prepare: the rotated width must be even and at most rope");
-  ROOST_REQUIRE(q && inv_freq && positions, "latent_prepare: a pointer is null");
+  ROOST_REQUIRE(tokens >= 0 && heads > 0 && nope > 0 && rope >= 0 && rank > 0, "latent_prepare: sizes must be positive");
+  ROOST_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= rope, "latent_prepare: the rotated width must be even and at most rope");
+  ROOST_REQUIRE(q && (inv_freq || rot_dims == 0) && positions, "latent_prepare: a pointer is null");
   ROOST_REQUIRE(down == nullptr || (pool && latent_w && slot_mapping && eps > 0.f), "latent_prepare: a latent needs its pool, weight, slots and eps");
   if (tokens == 0) return ROOST_OK;
   const size_t smem = ((size_t)rot_dims + 32) * sizeof(float);
@@ -218,7 +218,7 @@ extern "C" int roost_latent_attention(const void* q_latent, const void* q, void*
                                       const int32_t* token_row, const int32_t* kv_indptr, const int32_t* kv_indices, int tokens, int heads,
                                       int nope, int rope, int rank, int page_size, float scale, int window, int splits, int dtype,
                                       roost_stream_t stream) {
-  ROOST_REQUIRE(tokens >= 0 && heads > 0 && nope > 0 && rope > 0 && rank > 0 && page_size > 0, "latent_attention: sizes must be positive");
+  ROOST_REQUIRE(tokens >= 0 && heads > 0 && nope > 0 && rope >= 0 && rank > 0 && page_size > 0, "latent_attention: sizes must be positive");
   ROOST_REQUIRE(splits >= 1 && (splits == 1 || part != nullptr), "latent_attention: splits need a workspace for their partials");
   if (rank > kLaMaxRank) return fail(ROOST_ERR_UNSUPPORTED, "latent_attention: a latent of more than 1024 numbers");
   if (splits > 65535 || (heads + kLaWarps - 1) / kLaWarps > 65535) return fail(ROOST_ERR_UNSUPPORTED, "latent_attention: too many heads or splits");

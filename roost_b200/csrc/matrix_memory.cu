@@ -17,7 +17,8 @@
 // (S', n', m', F), one thread an entry then carries the row's memory from chunk to chunk leaving every chunk's true starting
 // memory in its place, and a second walk of every chunk from there writes the outputs and, from a row's last chunk, the slot.
 //
-// head_norm_gate: per token and head, o / sqrt(mean(o^2) + eps) * w * sigmoid(g), rounded once.
+// head_norm_gate: per token and head, o / sqrt(mean(o^2) + eps) * w * sigmoid(g) (w may be absent; with gate_silu the gate is
+// g sigmoid(g)), rounded once.
 #include "common.cuh"
 
 namespace roost {
@@ -230,7 +231,7 @@ __global__ void matrix_memory_carry_kernel(const float* state, int64_t state_str
 
 template <typename T>
 __global__ void head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ u, int64_t ld_u, int col, const float* __restrict__ w,
-                                      T* __restrict__ out, int heads, int vdim, float eps) {
+                                      T* __restrict__ out, int heads, int vdim, float eps, int gate_silu) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t t = blockIdx.x;
@@ -244,7 +245,8 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const T* __re
     for (int i = lane; i < vdim; i += 32) {
       const size_t c = (size_t)h * vdim + i;
       const float g = to_float(u[t * ld_u + col + c]);
-      out[t * heads * vdim + c] = from_float<T>(x[i] * inv * w[c] / (1.0f + expf(-g)));
+      const float y = x[i] * inv * (w != nullptr ? w[c] : 1.0f) / (1.0f + expf(-g));
+      out[t * heads * vdim + c] = from_float<T>(gate_silu ? y * g : y);
     }
   }
 }
@@ -302,12 +304,12 @@ extern "C" int roost_matrix_memory_scan(const void* qkv, int64_t ld, const float
 }
 
 extern "C" int roost_head_norm_gate(const float* o, const void* u, int64_t ld_u, int col, const float* w, void* out, int tokens, int heads, int vdim,
-                                    float eps, int dtype, roost_stream_t stream) {
+                                    float eps, int gate_silu, int dtype, roost_stream_t stream) {
   ROOST_REQUIRE(tokens >= 0 && heads > 0 && vdim > 0 && eps > 0.f && col >= 0 && ld_u >= col + (int64_t)heads * vdim, "head_norm_gate: sizes do not fit");
-  ROOST_REQUIRE(o && u && w && out, "head_norm_gate: a pointer is null");
+  ROOST_REQUIRE(o && u && out, "head_norm_gate: a pointer is null");
   if (tokens == 0) return ROOST_OK;
   const int threads = heads >= 8 ? 256 : (heads >= 4 ? 128 : 32 * heads);
   ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(head_norm_gate_kernel<T>, dim3(tokens), dim3(threads), 0, (cudaStream_t)stream, o, (const T*)u, ld_u, col,
-                                               w, (T*)out, heads, vdim, eps));
+                                               w, (T*)out, heads, vdim, eps, gate_silu));
   return check_launch("head_norm_gate");
 }

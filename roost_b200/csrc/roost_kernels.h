@@ -17,7 +17,7 @@
 extern "C" {
 #endif
 
-#define ROOST_ABI_VERSION 14
+#define ROOST_ABI_VERSION 15
 
 #define ROOST_OK 0
 #define ROOST_ERR_INVALID 1      /* an argument is out of range or inconsistent; nothing was launched */
@@ -401,6 +401,10 @@ int roost_mamba1_scan(const void* xc, const float* dt_raw, const void* dbc, int6
  * sqrt(mean(s^2) + eps) * w, or s where w is null. */
 int roost_wide_rms_norm(float* stream, const void* addend, const float* extra, const float* w, void* out, const int32_t* rows, int n_out,
                         int hidden, float eps, int dtype, roost_stream_t stream_handle);
+/* The same with the addend multiplied element by element by sigmoid(gate + gate_bias) first (gate: float32 [rows, hidden]). */
+int roost_wide_rms_norm_gated(float* stream, const void* addend, const float* gate, const float* gate_bias, const float* w, void* out,
+                              const int32_t* rows, int n_out, int hidden, float eps, int dtype, roost_stream_t stream_handle);
+int roost_scale(float* x, int64_t n, float factor, roost_stream_t stream);   /* x *= factor */
 /* out = mean over the n (1 to 4) branches of xs[b] / sqrt(mean(xs[b]^2) + eps) * ws[b]. */
 int roost_normed_mean(const void* const* xs, const float* const* ws, int n, void* out, int tokens, int hidden, float eps, int dtype,
                       roost_stream_t stream);
@@ -434,9 +438,40 @@ int roost_matrix_memory_scan_chunks(int tokens, int rows);
 int roost_matrix_memory_scan(const void* qkv, int64_t ld, const float* gates, float* out, float* state, int64_t state_stride,
                              const int32_t* q_indptr, const int32_t* slots, int rows, int tokens, int heads, int dim, int vdim, float cap,
                              float floor_, float* ws, int dtype, roost_stream_t stream);
-/* out = o / sqrt(mean over a head of o^2 + eps) * w * sigmoid(u[:, col:]). */
+/* out = o / sqrt(mean over a head of o^2 + eps) * w * sigmoid(u[:, col:]); w may be null (no weight); gate_silu: the gate is
+ * g sigmoid(g) instead. */
 int roost_head_norm_gate(const float* o, const void* u, int64_t ld_u, int col, const float* w, void* out, int tokens, int heads, int vdim,
-                         float eps, int dtype, roost_stream_t stream);
+                         float eps, int gate_silu, int dtype, roost_stream_t stream);
+
+/* ---- retention (retention.cu): S <- decay_h S + k v^T, o = S^T q a head; the slot holds S [heads, dim, vdim] ---- */
+/* qk (float32 [tokens, 2 * heads * dim]) = the rotated query heads and the rotated, scaled key heads of rows [q heads | k heads | ...]. */
+int roost_retention_prepare(const void* u, int64_t ld, float* qk, const double* inv_freq, const int32_t* positions, int tokens, int heads,
+                            int dim, int rot_dims, float k_scale, int dtype, roost_stream_t stream);
+/* ws: float[roost_retention_scan_chunks(tokens, rows) * heads * dim * vdim], or null. With it the rows are cut into chunks of 64 tokens
+ * that run side by side. v: the values' first column in rows ldv apart; out float32 [tokens, heads * vdim]. */
+int roost_retention_scan_chunks(int tokens, int rows);
+int roost_retention_scan(const float* qk, const void* v, int64_t ldv, float* out, float* state, int64_t state_stride, const float* decay,
+                         const int32_t* q_indptr, const int32_t* slots, int rows, int tokens, int heads, int dim, int vdim, float* ws, int dtype,
+                         roost_stream_t stream);
+
+/* ---- attention with sigmoid weights (sigmoid_attention.cu) ---- */
+/* Queries and keys divided by their root mean square times q_w / k_w (dim numbers each); queries times
+ * 1 + temp_coef * ln(floor((position + 1) / temp_every) + 1) into q_out [tokens, heads, dim]; keys and values into the cache. */
+int roost_sigmoid_attention_prepare(const void* qkv, int64_t ld, void* q_out, void* k_base, void* v_base, int entry, const float* q_w,
+                                    const float* k_w, const int32_t* positions, const int32_t* slot_mapping, int tokens, int heads, int kv_heads,
+                                    int dim, int vdim, float eps, float temp_coef, int temp_every, int page_size, int dtype, roost_stream_t stream);
+/* out[t, h] = sum over j <= p of sigmoid((q . k_j) scale - slopes[h] (p - j) + head_bias[h]) v_j, times sigmoid(gate[t, h, :]) where gate is
+ * not null (rows ld_gate apart). part: float[tokens * heads * splits * vdim] when splits > 1. */
+int roost_sigmoid_attention(const void* q, void* out, float* part, const void* k_base, const void* v_base, int entry, const void* gate,
+                            int64_t ld_gate, const float* slopes, const float* head_bias, const int32_t* positions, const int32_t* token_row,
+                            const int32_t* kv_indptr, const int32_t* kv_indices, int tokens, int heads, int kv_heads, int dim, int vdim,
+                            int page_size, float scale, int splits, int tiles_per_split, int dtype, roost_stream_t stream);
+
+/* ---- activations.cu ---- */
+/* y = a_pos z^2 + z / 2 (z > 0), a_neg (exp(z) - 1 - z) + z / 2 (z <= 0). */
+int roost_xielu(const void* x, void* out, int64_t n, float a_pos, float a_neg, int dtype, roost_stream_t stream);
+/* x[t, h, :] *= sigmoid(g[t, col + h]) in place; g's rows are ld_g apart. */
+int roost_head_gate_mul(void* x, const void* g, int64_t ld_g, int col, int tokens, int heads, int vdim, int dtype, roost_stream_t stream);
 
 #ifdef __cplusplus
 }

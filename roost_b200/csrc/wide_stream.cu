@@ -57,9 +57,12 @@ __global__ void layer_norm_kernel(float* stream, const T* __restrict__ addend, c
 // Root-mean-square norm over a 32-bit stream. One block per output row. s = stream + addend (activation dtype, may be null)
 // + extra (32-bit, may be null), each sum in 32-bit; s is written back to the stream unless the rows are gathered; the output is
 // s / sqrt(mean(s^2) + eps) * w, or s itself where w is null, rounded once.
+// With gate (32-bit, [rows, hidden]) the addend is first multiplied element by element by sigmoid(gate + gate_bias): a sublayer's
+// output scaled by a gate that was computed from the sublayer's own input.
 template <typename T>
 __global__ void wide_rms_norm_kernel(float* stream, const T* __restrict__ addend, const float* __restrict__ extra, const float* __restrict__ w,
-                                     T* __restrict__ out, const int32_t* __restrict__ rows, int hidden, float eps) {
+                                     T* __restrict__ out, const int32_t* __restrict__ rows, int hidden, float eps,
+                                     const float* __restrict__ gate, const float* __restrict__ gate_bias) {
   extern __shared__ float row[];  // hidden floats, then 32 floats of reduction scratch
   float* scratch = row + hidden;
   pdl_launch_dependents();
@@ -69,7 +72,11 @@ __global__ void wide_rms_norm_kernel(float* stream, const T* __restrict__ addend
   float ss = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float v = stream[r * hidden + i];
-    if (addend) v += to_float(addend[r * hidden + i]);
+    if (addend) {
+      float a = to_float(addend[r * hidden + i]);
+      if (gate) a *= 1.0f / (1.0f + expf(-(gate[r * hidden + i] + gate_bias[i])));
+      v += a;
+    }
     if (extra) v += extra[r * hidden + i];
     if ((addend || extra) && !rows) stream[r * hidden + i] = v;
     row[i] = v;
@@ -219,6 +226,13 @@ __global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap, float
   if (i < n) x[i] = cap * tanhf(x[i] * inv_cap);
 }
 
+__global__ void scale_kernel(float* __restrict__ x, size_t n, float factor) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] *= factor;
+}
+
 }  // namespace roost
 
 using namespace roost;
@@ -270,9 +284,37 @@ extern "C" int roost_wide_rms_norm(float* stream, const void* addend, const floa
   ROOST_DISPATCH_DTYPE(dtype, T, {
     auto kernel = wide_rms_norm_kernel<T>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_kernel(kernel, dim3(n_out), dim3(threads), smem, (cudaStream_t)stream_handle, stream, (const T*)addend, extra, w, (T*)out, rows, hidden, eps);
+    launch_kernel(kernel, dim3(n_out), dim3(threads), smem, (cudaStream_t)stream_handle, stream, (const T*)addend, extra, w, (T*)out, rows, hidden, eps,
+                  (const float*)nullptr, (const float*)nullptr);
   });
   return check_launch("wide_rms_norm");
+}
+
+extern "C" int roost_wide_rms_norm_gated(float* stream, const void* addend, const float* gate, const float* gate_bias, const float* w, void* out,
+                                         const int32_t* rows, int n_out, int hidden, float eps, int dtype, roost_stream_t stream_handle) {
+  ROOST_REQUIRE(n_out >= 0 && hidden > 0, "wide_rms_norm_gated: rows and hidden must be positive");
+  ROOST_REQUIRE(eps > 0.f, "wide_rms_norm_gated: eps must be positive");
+  ROOST_REQUIRE(stream && addend && gate && gate_bias && out, "wide_rms_norm_gated: a pointer is null");
+  if (n_out == 0) return ROOST_OK;
+  const size_t smem = ((size_t)hidden + 32) * sizeof(float);
+  if (smem > 200 * 1024) return fail(ROOST_ERR_UNSUPPORTED, "wide_rms_norm_gated: a row of more than 51168 elements does not fit in shared memory");
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  ROOST_DISPATCH_DTYPE(dtype, T, {
+    auto kernel = wide_rms_norm_kernel<T>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_kernel(kernel, dim3(n_out), dim3(threads), smem, (cudaStream_t)stream_handle, stream, (const T*)addend, (const float*)nullptr, w, (T*)out,
+                  rows, hidden, eps, gate, gate_bias);
+  });
+  return check_launch("wide_rms_norm_gated");
+}
+
+extern "C" int roost_scale(float* x, int64_t n, float factor, roost_stream_t stream) {
+  ROOST_REQUIRE(n >= 0 && (n == 0 || x), "scale: a pointer is null");
+  if (n == 0) return ROOST_OK;
+  const int64_t blocks = (n + 255) / 256;
+  if (blocks > 2147483647LL) return fail(ROOST_ERR_UNSUPPORTED, "scale: too many numbers for one launch");
+  launch_kernel(scale_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, x, (size_t)n, factor);
+  return check_launch("scale");
 }
 
 extern "C" int roost_normed_mean(const void* const* xs, const float* const* ws, int n, void* out, int tokens, int hidden, float eps, int dtype,

@@ -14,7 +14,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 14
+ABI_VERSION = 15
 F32, BF16 = 0, 1
 GATE_FUNCTIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}   # the codes of csrc/roost_kernels.h
 
@@ -157,7 +157,19 @@ _SIGNATURES = {
     "roost_matrix_memory_scan_chunks": [c_int, c_int],
     "roost_matrix_memory_scan": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                  c_float, c_float, c_void_p, c_int, c_void_p],
-    "roost_head_norm_gate": [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "roost_head_norm_gate": [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+    "roost_retention_prepare": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "roost_retention_scan_chunks": [c_int, c_int],
+    "roost_retention_scan": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                             c_void_p, c_int, c_void_p],
+    "roost_sigmoid_attention_prepare": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                        c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_void_p],
+    "roost_sigmoid_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
+    "roost_xielu": [c_void_p, c_void_p, c_int64, c_float, c_float, c_int, c_void_p],
+    "roost_head_gate_mul": [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "roost_wide_rms_norm_gated": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+    "roost_scale": [c_void_p, c_int64, c_float, c_void_p],
     "roost_mamba1_scan": [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
     "roost_mamba1_scan_chunks": [c_int, c_int],
@@ -599,16 +611,18 @@ class KernelLibrary:
     # ------------------------------------------------------------------ latent attention
     def latent_prepare(self, q, down, pool, latent_w, inv_freq, rotary_dim, positions, slot_mapping, heads, nope, rope, rank, eps, page_size) -> None:
         """Rotates the heads' rotated query parts in place and, when ``down`` is given, writes the tokens' cache entries."""
-        _need(q, "q"); _need(inv_freq, "inv_freq", torch.float64); _need(positions, "positions", torch.int32)
+        _need(q, "q"); _need(positions, "positions", torch.int32)
+        if rotary_dim:
+            _need(inv_freq, "inv_freq", torch.float64)
         T = q.shape[0]
-        if q.shape[1] != heads * (nope + rope) or inv_freq.numel() != rotary_dim // 2:
+        if q.shape[1] != heads * (nope + rope) or (rotary_dim and inv_freq.numel() != rotary_dim // 2):
             raise KernelError("latent_prepare: q or inv_freq do not fit the sizes")
         if down is not None:
             _need(down, "down", q.dtype); _need(pool, "pool", q.dtype); _need(latent_w, "latent_w", torch.float32)
             _need(slot_mapping, "slot_mapping", torch.int32)
             if tuple(down.shape) != (T, rank + rope) or tuple(pool.shape[1:]) != (1, page_size, rank + rope) or latent_w.numel() != rank:
                 raise KernelError("latent_prepare: down, pool or the latent's weight do not fit the sizes")
-        self._call("roost_latent_prepare", _ptr(q), _ptr(down), _ptr(pool), _ptr(latent_w), _ptr(inv_freq), _ptr(positions), _ptr(slot_mapping),
+        self._call("roost_latent_prepare", _ptr(q), _ptr(down), _ptr(pool), _ptr(latent_w), _ptr(inv_freq) if rotary_dim else None, _ptr(positions), _ptr(slot_mapping),
                    T, heads, nope, rope, rotary_dim, rank, eps, dtype_code(q.dtype), _stream())
 
     def latent_splits_for(self, tokens: int, heads: int, window: int | None, kv_cap: int) -> int:
@@ -1033,13 +1047,137 @@ class KernelLibrary:
                    launches=3 if ws is not None else 1)
         return out
 
-    def head_norm_gate(self, o, u, col: int, w, heads: int, eps: float, out_dtype) -> torch.Tensor:
-        """o / sqrt(mean over a head of o^2 + eps) * w * sigmoid(u[:, col : col + width]) into ``out_dtype``."""
-        _need(o, "o", torch.float32); _need(u, "u", out_dtype); _need(w, "w", torch.float32)
+    def head_norm_gate(self, o, u, col: int, w, heads: int, eps: float, out_dtype, gate: str = "sigmoid") -> torch.Tensor:
+        """o / sqrt(mean over a head of o^2 + eps) * w * sigmoid(u[:, col : col + width]) into ``out_dtype``; ``w`` None: no weight;
+        ``gate`` "silu": the gate is g sigmoid(g) of g = u[:, col : col + width]."""
+        if gate not in ("sigmoid", "silu"):
+            raise KernelError(f"head_norm_gate: gate '{gate}' is neither sigmoid nor silu")
+        _need(o, "o", torch.float32); _need(u, "u", out_dtype)
+        if w is not None:
+            _need(w, "w", torch.float32)
         T, V = o.shape
         out = torch.empty((T, V), dtype=out_dtype, device=o.device)
-        self._call("roost_head_norm_gate", _ptr(o), _ptr(u), u.stride(0), col, _ptr(w), _ptr(out), T, heads, V // heads, eps, dtype_code(out_dtype), _stream())
+        self._call("roost_head_norm_gate", _ptr(o), _ptr(u), u.stride(0), col, _ptr(w), _ptr(out), T, heads, V // heads, eps,
+                   1 if gate == "silu" else 0, dtype_code(out_dtype), _stream())
         return out
+
+    # ------------------------------------------------------------------ retention
+    def retention_prepare(self, u, inv_freq, rotary_dim: int, positions, heads: int, dim: int, k_scale: float) -> torch.Tensor:
+        """The rotated query heads and the rotated, scaled key heads of rows [q heads | k heads | ...] as float32 [T, 2 * heads * dim]."""
+        _need(u, "u"); _need(positions, "positions", torch.int32)
+        if rotary_dim:
+            _need(inv_freq, "inv_freq", torch.float64)
+            if inv_freq.numel() != rotary_dim // 2:
+                raise KernelError("retention_prepare: inv_freq must have rotary_dim / 2 entries")
+        T = u.shape[0]
+        if u.shape[1] < 2 * heads * dim:
+            raise KernelError("retention_prepare: the rows do not hold the query and key heads")
+        qk = torch.empty((T, 2 * heads * dim), dtype=torch.float32, device=u.device)
+        self._call("roost_retention_prepare", _ptr(u), u.stride(0), _ptr(qk), _ptr(inv_freq) if rotary_dim else None, _ptr(positions), T, heads, dim,
+                   rotary_dim, float(k_scale), dtype_code(u.dtype), _stream())
+        return qk
+
+    def retention_scan(self, qk, u, v_col: int, state, decay, q_indptr, slots, heads: int, dim: int, vdim: int, chunked: bool | None = None) -> torch.Tensor:
+        """S <- decay_h S + k v^T, o = S^T q a head: float32 [T, heads * vdim]; see csrc/retention.cu. The values are the columns
+        from ``v_col`` on of ``u``. ``chunked`` None: steps of ``SCAN_CHUNKED_MIN_TOKENS`` tokens or more cut their rows into chunks."""
+        _need(qk, "qk", torch.float32); _need(u, "u"); _need(state, "state", torch.float32); _need(decay, "decay", torch.float32)
+        _need(q_indptr, "q_indptr", torch.int32); _need(slots, "slots", torch.int32)
+        T = u.shape[0]
+        if tuple(qk.shape) != (T, 2 * heads * dim) or u.shape[1] < v_col + heads * vdim or decay.numel() != heads:
+            raise KernelError("retention_scan: the queries and keys, the values or the decays do not fit the sizes")
+        out = torch.empty((T, heads * vdim), dtype=torch.float32, device=u.device)
+        ws = None
+        if (T >= self.SCAN_CHUNKED_MIN_TOKENS) if chunked is None else chunked:
+            chunks = self._lib.roost_retention_scan_chunks(T, slots.numel())
+            ws = torch.empty((chunks * heads * dim * vdim,), dtype=torch.float32, device=u.device)
+        self._call("roost_retention_scan", _ptr(qk), u.data_ptr() + v_col * u.element_size(), u.stride(0), _ptr(out), _ptr(state), state.stride(0),
+                   _ptr(decay), _ptr(q_indptr), _ptr(slots), slots.numel(), T, heads, dim, vdim, _ptr(ws), dtype_code(u.dtype), _stream(),
+                   launches=3 if ws is not None else 1)
+        return out
+
+    # ------------------------------------------------------------------ attention with sigmoid weights
+    def sigmoid_attention_prepare(self, qkv, k_pool, v_pool, q_w, k_w, positions, slot_mapping, heads, kv_heads, dim, vdim, eps, temp_coef,
+                                  temp_every, page_size) -> torch.Tensor:
+        """Normed (and, for the queries, temperature-scaled) heads: the queries come back as [T, heads, dim], keys and values go to the cache."""
+        _need(qkv, "qkv"); _need(k_pool, "k_pool", qkv.dtype); _need(positions, "positions", torch.int32); _need(slot_mapping, "slot_mapping", torch.int32)
+        _need(q_w, "q_w", torch.float32); _need(k_w, "k_w", torch.float32)
+        if v_pool is not None:
+            _need(v_pool, "v_pool", qkv.dtype)
+        if qkv.shape[1] < (heads + kv_heads) * dim + kv_heads * vdim or k_pool.shape[1] != kv_heads or k_pool.shape[2] != page_size:
+            raise KernelError("sigmoid_attention_prepare: qkv or the pool do not fit the sizes")
+        if q_w.numel() != dim or k_w.numel() != dim:
+            raise KernelError("sigmoid_attention_prepare: the norms' weights must have dim entries")
+        kb, vb, entry = self._sink_cache(k_pool, v_pool, dim, vdim)
+        q = torch.empty((qkv.shape[0], heads, dim), dtype=qkv.dtype, device=qkv.device)
+        self._call("roost_sigmoid_attention_prepare", _ptr(qkv), qkv.stride(0), _ptr(q), kb, vb, entry, _ptr(q_w), _ptr(k_w), _ptr(positions),
+                   _ptr(slot_mapping), qkv.shape[0], heads, kv_heads, dim, vdim, float(eps), float(temp_coef), int(temp_every), page_size,
+                   dtype_code(qkv.dtype), _stream())
+        return q
+
+    def sigmoid_attention(self, q, k_pool, v_pool, gate_rows, gate_col, slopes, head_bias, positions, token_row, kv_indptr, kv_indices, kv_heads, vdim,
+                          scale, kv_cap: int = 0) -> torch.Tensor:
+        """out[t, h] = sum over visible keys j of sigmoid((q . k_j) scale - slopes[h] (p - j) + head_bias[h]) v_j, times
+        sigmoid(gate_rows[t, gate_col + h * vdim : ...]) when ``gate_col`` is not None: [T, heads * vdim]."""
+        _need(q, "q"); _need(k_pool, "k_pool", q.dtype); _need(slopes, "slopes", torch.float32); _need(head_bias, "head_bias", torch.float32)
+        for n, t in (("positions", positions), ("token_row", token_row), ("kv_indptr", kv_indptr), ("kv_indices", kv_indices)):
+            _need(t, n, torch.int32)
+        T, heads, dim = q.shape
+        if slopes.numel() != heads or head_bias.numel() != heads:
+            raise KernelError("sigmoid_attention: one slope and one bias a query head")
+        gate_ptr, ld_gate = None, 0
+        if gate_col is not None:
+            _need(gate_rows, "gate_rows", q.dtype)
+            if gate_rows.shape[0] != T or gate_rows.shape[1] < gate_col + heads * vdim:
+                raise KernelError("sigmoid_attention: the gate's rows do not fit the sizes")
+            gate_ptr, ld_gate = gate_rows.data_ptr() + gate_col * gate_rows.element_size(), gate_rows.stride(0)
+        kb, vb, entry = self._sink_cache(k_pool, v_pool, dim, vdim)
+        out = torch.empty((T, heads * vdim), dtype=q.dtype, device=q.device)
+        gy = kv_heads * (-(-(heads // kv_heads) // 8))
+        splits, per = self.sink_splits_for(T, gy, kv_cap) if kv_cap else (1, 1 << 24)
+        part = torch.empty((T * heads * splits * vdim,), dtype=torch.float32, device=q.device) if splits > 1 else None
+        self._call("roost_sigmoid_attention", _ptr(q), _ptr(out), _ptr(part), kb, vb, entry, gate_ptr, ld_gate, _ptr(slopes), _ptr(head_bias),
+                   _ptr(positions), _ptr(token_row), _ptr(kv_indptr), _ptr(kv_indices), T, heads, kv_heads, dim, vdim, k_pool.shape[2], float(scale),
+                   splits, per, dtype_code(q.dtype), _stream(), launches=2 if splits > 1 else 1)
+        return out
+
+    # ------------------------------------------------------------------ activations, gates, scaled sums
+    def xielu(self, x: torch.Tensor, a_pos: float, a_neg: float) -> torch.Tensor:
+        """a_pos z^2 + z / 2 for z > 0, a_neg (exp(z) - 1 - z) + z / 2 for z <= 0."""
+        _need(x, "x")
+        out = torch.empty_like(x)
+        self._call("roost_xielu", _ptr(x), _ptr(out), x.numel(), float(a_pos), float(a_neg), dtype_code(x.dtype), _stream())
+        return out
+
+    def head_gate_mul_(self, x: torch.Tensor, g: torch.Tensor, col: int, heads: int) -> torch.Tensor:
+        """x[t, h, :] *= sigmoid(g[t, col + h]) in place, for x [T, heads * vdim]."""
+        _need(x, "x"); _need(g, "g", x.dtype)
+        T, V = x.shape
+        if V % heads or g.shape[0] != T or g.shape[1] < col + heads:
+            raise KernelError("head_gate_mul: one gate a token and head")
+        self._call("roost_head_gate_mul", _ptr(x), _ptr(g), g.stride(0), col, T, heads, V // heads, dtype_code(x.dtype), _stream())
+        return x
+
+    def wide_rms_norm_gated(self, stream, w, eps: float, out_dtype, addend, gate, gate_bias, rows=None) -> torch.Tensor:
+        """``wide_rms_norm`` with the addend multiplied by sigmoid(gate + gate_bias) first (gate float32 like the stream, bias [hidden])."""
+        _need(stream, "stream", torch.float32); _need(addend, "addend", out_dtype); _need(gate, "gate", torch.float32)
+        _need(gate_bias, "gate_bias", torch.float32)
+        H = stream.shape[-1]
+        if w is not None:
+            _need(w, "w", torch.float32)
+        if addend.shape != stream.shape or gate.shape != stream.shape or gate_bias.numel() != H or (w is not None and w.numel() != H):
+            raise KernelError("wide_rms_norm_gated: the addend, the gate, its bias or the weight do not fit the stream")
+        if rows is not None:
+            _need(rows, "rows", torch.int32)
+        n = stream.numel() // H if rows is None else rows.numel()
+        out = torch.empty((n, H), dtype=out_dtype, device=stream.device)
+        self._call("roost_wide_rms_norm_gated", _ptr(stream), _ptr(addend), _ptr(gate), _ptr(gate_bias), _ptr(w), _ptr(out), _ptr(rows), n, H, eps,
+                   dtype_code(out_dtype), _stream())
+        return out
+
+    def scale_(self, x: torch.Tensor, factor: float) -> torch.Tensor:
+        _need(x, "x", torch.float32)
+        self._call("roost_scale", _ptr(x), x.numel(), float(factor), _stream())
+        return x
 
     # ------------------------------------------------------------------ the selective scan
     def mamba1_scan(self, xc, dt, dbc, xz, dt_bias, a, d, state, q_indptr, slots, inner, n_state, dt_rank, chunked: bool | None = None) -> torch.Tensor:

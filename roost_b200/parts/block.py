@@ -105,6 +105,74 @@ class PreNormWideBlock(Block):
         return a, residual
 
 
+class GatedStream:
+    """The 32-bit residual between two sublayers of a gated arrangement, and the gate (arguments, bias) that the branch output
+    travelling beside it is still to be multiplied by when it is added."""
+    __slots__ = ("stream", "gate")
+
+    def __init__(self, stream, gate):
+        self.stream, self.gate = stream, gate
+
+
+class PreNormGatedBlock(Block):
+    """x <- x + mixer(n1) sigmoid(W1 n1 + b1); x <- x + ff(n2) sigmoid(W2 n2 + b2), n = norm(x), over a residual kept and summed in
+    32-bit: a sublayer's gate is made from the sublayer's own normed input (``connection`` of kind ``sigmoid_gate``) and applied by
+    the kernel that adds the sublayer's output to the residual, the next norm's. The block hands on its last branch output and the
+    residual with the gate still to be applied; ``close`` does the last gated sum and the final norm of the wanted rows."""
+
+    def __init__(self, spec: BlockSpec, runtime: Runtime):
+        if spec.connection is None:
+            raise ValueError("pre_norm_gated: the block needs a connection that makes the gates")
+        self.spec = spec
+        self.rt = runtime
+        self.input_norm = NORMS.build(spec.input_norm, runtime)
+        self.mixer = MIXERS.build(spec.mixer, runtime)
+        self.mixer_connection = CONNECTIONS.build(spec.connection, runtime)
+        self.feed_forward = self.post_mixer_norm = self.feed_forward_connection = None
+        if spec.feed_forward is not None:
+            if spec.post_mixer_norm is None:
+                raise ValueError("pre_norm_gated: a feed-forward needs the norm before it")
+            self.post_mixer_norm = NORMS.build(spec.post_mixer_norm, runtime)
+            self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, runtime)
+            self.feed_forward_connection = CONNECTIONS.build(spec.connection, runtime)
+
+    def sub_parts(self):
+        parts = {"input_norm": self.input_norm, "mixer": self.mixer, "mixer_connection": self.mixer_connection}
+        if self.feed_forward is not None:
+            parts.update({"post_mixer_norm": self.post_mixer_norm, "feed_forward": self.feed_forward,
+                          "feed_forward_connection": self.feed_forward_connection})
+        return parts
+
+    @classmethod
+    def sub_specs(cls, spec: BlockSpec):
+        subs = {"input_norm": (NORMS, spec.input_norm), "mixer": (MIXERS, spec.mixer), "mixer_connection": (CONNECTIONS, spec.connection)}
+        if spec.feed_forward is not None:
+            subs.update({"post_mixer_norm": (NORMS, spec.post_mixer_norm), "feed_forward": (FEED_FORWARDS, spec.feed_forward),
+                         "feed_forward_connection": (CONNECTIONS, spec.connection)})
+        return subs
+
+    def __call__(self, h, residual, batch, cache, write_cache: bool = True):
+        if residual is None:
+            if h.dtype != torch.float32:
+                raise ValueError("pre_norm_gated: the embedding must hand over a float32 stream")
+            stream = h
+            x = self.input_norm(h)
+        else:
+            stream = residual.stream
+            x, _ = self.input_norm.add_norm(h, stream, gate=residual.gate)
+        gate = (self.mixer_connection.arguments(x), self.mixer_connection.bias)
+        a = self.mixer(x, batch, cache, write_cache)
+        if self.feed_forward is not None:
+            y, _ = self.post_mixer_norm.add_norm(a, stream, gate=gate)
+            gate = (self.feed_forward_connection.arguments(y), self.feed_forward_connection.bias)
+            a = self.feed_forward(y, batch)
+        return a, GatedStream(stream, gate)
+
+    def close(self, h, residual, norm, rows):
+        """The model's end: the last gated sum of the wanted rows and ``norm`` of it."""
+        return norm.add_norm(h, residual.stream, rows=rows, gate=residual.gate)[0]
+
+
 class StreamState:
     """The residual streams between two sublayers: the 32-bit tensor [tokens, streams, width] and the connection whose
     write-back of the branch output that travels beside it is still to be applied."""
@@ -178,5 +246,6 @@ class PreNormStreamsBlock(Block):
 
 
 register_block("pre_norm_streams", PreNormStreamsBlock)
+register_block("pre_norm_gated", PreNormGatedBlock)
 register_block("pre_norm", PreNormBlock)
 register_block("pre_norm_wide", PreNormWideBlock)

@@ -12,8 +12,9 @@ from __future__ import annotations
 
 import torch
 
-from ..config.spec import ConnectionSpec
+from ..config.spec import ConnectionSpec, GatedResidualSpec
 from .base import Connection, ParamDecl, Runtime, register_connection
+from .linear import Linear
 
 MAX_STREAMS = 8     # the kernel keeps a channel's streams in registers
 
@@ -49,3 +50,30 @@ class HyperConnection(Connection):
 
 
 register_connection("hyper_connection", HyperConnection)
+
+
+class SigmoidGate(Connection):
+    """x <- x + y sigmoid(W h + b): a sublayer's output y scaled element by element by a gate made from the sublayer's own input h.
+    ``arguments(h)`` gives W h as 32-bit sums; the bias, the sigmoid and the product with y belong to the kernel that adds y to the
+    32-bit residual (the next norm's), so the gated output is never rounded on its own."""
+
+    def __init__(self, spec: GatedResidualSpec, runtime: Runtime):
+        if spec.hidden <= 0:
+            raise ValueError("sigmoid_gate: hidden must be positive")
+        self.spec, self.rt = spec, runtime
+        self.linear = Linear(runtime, spec.hidden, spec.hidden)
+        self.bias = None
+
+    @classmethod
+    def parameters(cls, spec: GatedResidualSpec):
+        return {"gate": ParamDecl(shape=(spec.hidden, spec.hidden)), "gate_bias": ParamDecl(shape=(spec.hidden,), role="vector", init=("normal", 0.0, 0.5))}
+
+    def load(self, params):
+        self.linear.load(params["gate"])
+        self.bias = params["gate_bias"].float().contiguous()
+
+    def arguments(self, h: torch.Tensor) -> torch.Tensor:
+        return self.linear(h, out_dtype=torch.float32)
+
+
+register_connection("sigmoid_gate", SigmoidGate)

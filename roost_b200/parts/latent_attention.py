@@ -12,7 +12,9 @@ Per step: the q projection (and, for a run that makes its own latent, the down p
 the latent by its root mean square, rotates the shared key part and every head's rotated query part and writes the
 cache entry; the batched product into the latent space; attention; the batched product out of it; the output
 projection. A run that reads another run's cache makes no latent and writes nothing; its window may differ from the
-owner's (the cache is kept for the widest).
+owner's (the cache is kept for the widest). With ``rope_dim`` 0 keys and queries have no rotated part: nothing is rotated and the
+cache entry is the latent alone. With ``head_gate`` one more small projection gives a number a token and head, and a kernel
+multiplies every head's output by its sigmoid before the output projection.
 """
 from __future__ import annotations
 
@@ -26,8 +28,8 @@ from .linear import Linear, batched_linear
 class LatentAttention(Mixer):
     def __init__(self, spec: LatentAttentionSpec, runtime: Runtime):
         s = spec
-        if min(s.hidden, s.num_heads, s.nope_dim, s.rope_dim, s.v_dim, s.kv_rank) <= 0:
-            raise ValueError("latent_attention: hidden, heads, nope_dim, rope_dim, v_dim and kv_rank must be positive")
+        if min(s.hidden, s.num_heads, s.nope_dim, s.v_dim, s.kv_rank) <= 0 or s.rope_dim < 0:
+            raise ValueError("latent_attention: hidden, heads, nope_dim, v_dim and kv_rank must be positive and rope_dim not negative")
         if s.kv_rank + s.rope_dim > 1024:
             raise ValueError(f"latent_attention: a cache entry of {s.kv_rank + s.rope_dim} numbers is beyond 1024, the largest the kernel serves")
         if s.window is not None and s.window <= 0:
@@ -36,8 +38,10 @@ class LatentAttention(Mixer):
             raise ValueError(f"latent_attention: the window {s.window} reaches beyond what the cache keeps ({s.cache_window})")
         if s.scale <= 0:
             raise ValueError(f"latent_attention: scale {s.scale} must be positive")
-        if s.position is None or s.position.rotary_dim > s.rope_dim:
+        if s.rope_dim and (s.position is None or s.position.rotary_dim > s.rope_dim):
             raise ValueError("latent_attention: a rotation of at most rope_dim elements is needed")
+        if not s.rope_dim and s.position is not None and s.position.kind != "none":
+            raise ValueError("latent_attention: keys without a rotated part take no position encoding")
         self.spec = s
         self.rt = runtime
         self.q_head = s.nope_dim + s.rope_dim
@@ -45,7 +49,8 @@ class LatentAttention(Mixer):
         self.q = Linear(runtime, s.num_heads * self.q_head, s.hidden)
         self.down = Linear(runtime, self.entry, s.hidden) if s.own_latent else None
         self.out = Linear(runtime, s.hidden, s.num_heads * s.v_dim)
-        self.position = POSITIONS.build(s.position, runtime)
+        self.position = POSITIONS.build(s.position, runtime) if s.rope_dim else None
+        self.head_gate = Linear(runtime, s.num_heads, s.hidden) if s.head_gate else None
         self.key_up: torch.Tensor | None = None      # [heads, kv_rank, nope_dim]: W_uk,h^T as a weight stored [out, in]
         self.value_up: torch.Tensor | None = None    # [heads, v_dim, kv_rank]
         self.latent_weight: torch.Tensor | None = None
@@ -56,6 +61,8 @@ class LatentAttention(Mixer):
         p = {"q": ParamDecl(shape=(s.num_heads * (s.nope_dim + s.rope_dim), s.hidden)),
              "uk": ParamDecl(shape=(s.num_heads * s.nope_dim, s.kv_rank)), "uv": ParamDecl(shape=(s.num_heads * s.v_dim, s.kv_rank)),
              "out": ParamDecl(shape=(s.hidden, s.num_heads * s.v_dim))}
+        if s.head_gate:
+            p["head_gate"] = ParamDecl(shape=(s.num_heads, s.hidden))
         if s.own_latent:
             p["dkv"] = ParamDecl(shape=(s.kv_rank + s.rope_dim, s.hidden))
             p["latent_norm"] = ParamDecl(shape=(s.kv_rank,), role="vector")
@@ -67,6 +74,8 @@ class LatentAttention(Mixer):
         self.out.load(params["out"])
         self.key_up = params["uk"].to(self.rt.dtype).reshape(s.num_heads, s.nope_dim, s.kv_rank).transpose(1, 2).contiguous()
         self.value_up = params["uv"].to(self.rt.dtype).reshape(s.num_heads, s.v_dim, s.kv_rank).contiguous()
+        if s.head_gate:
+            self.head_gate.load(params["head_gate"])
         if s.own_latent:
             self.down.load(params["dkv"])
             self.latent_weight = params["latent_norm"].float().contiguous()
@@ -81,7 +90,7 @@ class LatentAttention(Mixer):
             raise ValueError("latent_attention: a run writes the cache exactly when it makes its own latent")
         tables = batch.groups[cache.group]
         T, H = x.shape[0], s.num_heads
-        inv_freq, rotary_dim = self.position.rotation()
+        inv_freq, rotary_dim = self.position.rotation() if self.position is not None else (None, 0)
         q = self.q(x)                                                       # [T, H * (nope + rope)]
         down = self.down(x) if s.own_latent else None                       # [T, kv_rank + rope]
         k.latent_prepare(q, down, cache.k_pool, self.latent_weight, inv_freq, rotary_dim, batch.positions,
@@ -93,6 +102,8 @@ class LatentAttention(Mixer):
                                       H, s.nope_dim, s.rope_dim, s.kv_rank, s.scale, s.window, batch.kv_cap, batch.all_single, batch.q_indptr)
         o = torch.empty((T, H * s.v_dim), dtype=q.dtype, device=q.device)
         batched_linear(self.rt, o_latent, self.value_up, o.view(T, H, s.v_dim).transpose(0, 1))
+        if s.head_gate:
+            k.head_gate_mul_(o, self.head_gate(x), 0, H)                     # head h's output times sigmoid((W_g x)_h)
         return self.out(o)
 
 

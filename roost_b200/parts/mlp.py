@@ -5,7 +5,9 @@ the tanh form of GELU, the clamped swish of routed designs) run the same product
 the function as an argument; the products that apply SiLU to their own sums serve "silu" only."""
 from __future__ import annotations
 
-from ..config.spec import GatedMlpSpec
+import math
+
+from ..config.spec import DenseMlpSpec, GatedMlpSpec
 from .base import FeedForward, ParamDecl, Runtime, register_feed_forward
 from .linear import Linear
 
@@ -83,4 +85,38 @@ class GatedMlp(FeedForward):
         return self.down(k.silu_mul(self.gate_up(x), self.interleave))
 
 
+class DenseMlp(FeedForward):
+    """down(act(x Wu^T)) without a gate. ``xielu``: two stored numbers (p, q) give a_pos = softplus(p) and a_neg = 1/2 + softplus(q),
+    formed once at load in double; act(z) = a_pos z^2 + z / 2 for z > 0 and a_neg (exp(z) - 1 - z) + z / 2 for z <= 0, on the 32-bit
+    value of the up projection's output, rounded once."""
+
+    ACTIVATIONS = ("xielu",)
+
+    def __init__(self, spec: DenseMlpSpec, runtime: Runtime):
+        if spec.hidden <= 0 or spec.intermediate <= 0:
+            raise ValueError("dense_mlp: hidden and intermediate must be positive")
+        if spec.activation not in self.ACTIVATIONS:
+            raise ValueError(f"dense_mlp: activation '{spec.activation}' has no kernel (built: {', '.join(self.ACTIVATIONS)})")
+        self.spec, self.rt = spec, runtime
+        self.up = Linear(runtime, spec.intermediate, spec.hidden)
+        self.down = Linear(runtime, spec.hidden, spec.intermediate)
+        self.a_pos = self.a_neg = 0.0
+
+    @classmethod
+    def parameters(cls, spec: DenseMlpSpec):
+        I, H = spec.intermediate, spec.hidden
+        return {"up": ParamDecl(shape=(I, H)), "down": ParamDecl(shape=(H, I)), "act": ParamDecl(shape=(2,), role="vector", init=("normal", 0.0, 0.5))}
+
+    def load(self, params):
+        self.up.load(params["up"])
+        self.down.load(params["down"])
+        p, q = (float(v) for v in params["act"].double().cpu())
+        softplus = lambda z: max(z, 0.0) + math.log1p(math.exp(-abs(z)))
+        self.a_pos, self.a_neg = softplus(p), 0.5 + softplus(q)
+
+    def __call__(self, x, batch=None):
+        return self.down(self.rt.kernels.xielu(self.up(x), self.a_pos, self.a_neg))
+
+
 register_feed_forward("gated_mlp", GatedMlp)
+register_feed_forward("dense_mlp", DenseMlp)

@@ -87,8 +87,14 @@ class WideRmsNorm(Norm):
     def __call__(self, x: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
         return self.rt.kernels.wide_rms_norm(x, self.weight, self.spec.eps, self.rt.dtype, None, None, rows)
 
-    def add_norm(self, x: torch.Tensor, residual: torch.Tensor, rows: torch.Tensor | None = None, extra: torch.Tensor | None = None):
-        """Returns (norm(residual + x [+ extra]), the sum); without ``rows`` the sum replaces ``residual`` in place."""
+    def add_norm(self, x: torch.Tensor, residual: torch.Tensor, rows: torch.Tensor | None = None, extra: torch.Tensor | None = None,
+                 gate: tuple | None = None):
+        """Returns (norm(residual + x [+ extra]), the sum); without ``rows`` the sum replaces ``residual`` in place. ``gate``
+        (arguments: float32 like x, bias: float32 [hidden]): x is multiplied by sigmoid(arguments + bias) before it is added."""
+        if gate is not None:
+            if extra is not None:
+                raise ValueError("rms_norm_wide: a gated sum takes no second addend")
+            return self.rt.kernels.wide_rms_norm_gated(residual, self.weight, self.spec.eps, self.rt.dtype, x, gate[0], gate[1], rows), residual
         return self.rt.kernels.wide_rms_norm(residual, self.weight, self.spec.eps, self.rt.dtype, x, extra, rows), residual
 
     def add_only(self, x: torch.Tensor, residual: torch.Tensor):

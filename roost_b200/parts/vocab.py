@@ -78,6 +78,14 @@ class CappedLinearHead(LinearHead):
         return self.rt.kernels.softcap_(self.linear(final, out_dtype=torch.float32), float(self.spec.cap))
 
 
+class ScaledLinearHead(LinearHead):
+    """logits * scale on the 32-bit logits."""
+
+    def __call__(self, final, batch=None):
+        logits = self.linear(final, out_dtype=torch.float32)
+        return logits if self.spec.scale == 1.0 else self.rt.kernels.scale_(logits, float(self.spec.scale))
+
+
 class PairHashedEmbedding(TableEmbedding):
     """h0[t, :] = table[id_t, :] + pairs[row_t, :] as a float32 stream, row_t = (id_(t-1) * mul_prev + id_t * mul_cur) mod
     buckets, and the row after the buckets for a request's first token. The token before a step's first token of a request
@@ -116,4 +124,5 @@ register_embedding("pair_hashed_table", PairHashedEmbedding)
 register_embedding("table", TableEmbedding)
 register_embedding("scaled_table", ScaledTableEmbedding)
 register_head("capped_linear", CappedLinearHead)
+register_head("scaled_linear", ScaledLinearHead)
 register_head("linear", LinearHead)

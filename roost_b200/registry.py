@@ -57,7 +57,8 @@ def resolve(reader: ConfigReader) -> Architecture:
 
 
 def _register_builtin() -> None:
-    from .config import lafanex, nomivik, qwen3, vamatar
+    from .config import lafanex, lovurax, nomivik, qwen3, vamatar
+    register_architecture(lovurax.ARCHITECTURE, read_config=lovurax.LovuraxConfig.from_reader, to_spec=lambda cfg, tied=None: cfg.to_spec(tied))
     register_architecture(nomivik.ARCHITECTURE, read_config=nomivik.NomivikConfig.from_reader, to_spec=lambda cfg, tied=None: cfg.to_spec(tied))
     register_architecture(lafanex.ARCHITECTURE, read_config=lafanex.LafanexConfig.from_reader, to_spec=lambda cfg, tied=None: cfg.to_spec(tied))
     register_architecture(vamatar.ARCHITECTURE, read_config=vamatar.VamatarConfig.from_reader, to_spec=lambda cfg, tied=None: cfg.to_spec(tied))

@@ -121,6 +121,8 @@ class FakeKernels:
     def latent_prepare(self, q, down, pool, latent_w, inv_freq, rotary_dim, positions, slot_mapping, heads, nope, rope, rank, eps, page_size):
         T = q.shape[0]
         half = rotary_dim // 2
+        if inv_freq is None:      # no rotated part
+            inv_freq = torch.zeros(0, dtype=torch.float64)
         ang = positions.double()[:, None] * inv_freq[None, :]
         c, s = torch.cos(ang).float(), torch.sin(ang).float()
 
@@ -457,11 +459,118 @@ class FakeKernels:
                 st.copy_(torch.cat([S.reshape(heads, -1), n, new[:, None]], dim=1))
         return out
 
-    def head_norm_gate(self, o, u, col, w, heads, eps, out_dtype):
+    def head_norm_gate(self, o, u, col, w, heads, eps, out_dtype, gate="sigmoid"):
         T, V = o.shape
         x = o.reshape(T, heads, V // heads)
-        x = (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps)).reshape(T, V) * w.float()
-        return (x * torch.sigmoid(u[:, col : col + V].float())).to(out_dtype)
+        x = (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps)).reshape(T, V)
+        if w is not None:
+            x = x * w.float()
+        g = u[:, col : col + V].float()
+        return (x * torch.sigmoid(g) * (g if gate == "silu" else 1.0)).to(out_dtype)
+
+    # ---- retention
+    def retention_prepare(self, u, inv_freq, rotary_dim, positions, heads, dim, k_scale):
+        T = u.shape[0]
+        x = u[:, : 2 * heads * dim].float().reshape(T, 2 * heads, dim).clone()
+        if rotary_dim:
+            half = rotary_dim // 2
+            ang = positions.double()[:, None] * inv_freq[None, :]
+            c, s = torch.cos(ang)[:, None, :].float(), torch.sin(ang)[:, None, :].float()
+            a, b = x[..., :half].clone(), x[..., half:rotary_dim].clone()
+            x[..., :half] = a * c - b * s
+            x[..., half:rotary_dim] = b * c + a * s
+        x[:, heads:] *= k_scale
+        return x.reshape(T, 2 * heads * dim)
+
+    def retention_scan(self, qk, u, v_col, state, decay, q_indptr, slots, heads, dim, vdim, chunked=None):
+        T = u.shape[0]
+        q = qk[:, : heads * dim].reshape(T, heads, dim)
+        k = qk[:, heads * dim :].reshape(T, heads, dim)
+        v = u[:, v_col : v_col + heads * vdim].float().reshape(T, heads, vdim)
+        out = torch.zeros(T, heads * vdim, dtype=torch.float32)
+        for row in range(slots.numel()):
+            lo, hi = int(q_indptr[row]), int(q_indptr[row + 1])
+            S = state[int(slots[row])].view(heads, dim, vdim)
+            for t in range(lo, hi):
+                S.copy_(decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :])
+                out[t] = torch.einsum("hdv,hd->hv", S, q[t]).reshape(-1)
+        return out
+
+    # ---- attention with sigmoid weights
+    def sigmoid_attention_prepare(self, qkv, k_pool, v_pool, q_w, k_w, positions, slot_mapping, heads, kv_heads, dim, vdim, eps, temp_coef, temp_every,
+                                  page_size):
+        T = qkv.shape[0]
+        Q, K = heads * dim, kv_heads * dim
+
+        def norm(x, w):
+            return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w.float()
+
+        temp = 1.0 + temp_coef * torch.log((torch.div(positions.clamp(min=0) + 1, temp_every, rounding_mode="floor") + 1).float())
+        q = (norm(qkv[:, :Q].float().reshape(T, heads, dim), q_w) * temp[:, None, None]).to(qkv.dtype)
+        k = norm(qkv[:, Q : Q + K].float().reshape(T, kv_heads, dim), k_w).to(qkv.dtype)
+        v = qkv[:, Q + K : Q + K + kv_heads * vdim].reshape(T, kv_heads, vdim)
+        for t in range(T):
+            slot = int(slot_mapping[t])
+            if slot < 0:
+                continue
+            page, off = divmod(slot, page_size)
+            if v_pool is None:
+                k_pool[page, :, off, :dim] = k[t]
+                k_pool[page, :, off, dim:] = v[t]
+            else:
+                k_pool[page, :, off, :] = k[t]
+                v_pool[page, :, off, :] = v[t]
+        return q.contiguous()
+
+    def sigmoid_attention(self, q, k_pool, v_pool, gate_rows, gate_col, slopes, head_bias, positions, token_row, kv_indptr, kv_indices, kv_heads, vdim,
+                          scale, kv_cap=0):
+        T, heads, dim = q.shape
+        page_size = k_pool.shape[2]
+        out = torch.zeros(T, heads * vdim, dtype=q.dtype)
+        group = heads // kv_heads
+        for t in range(T):
+            pos = int(positions[t])
+            if pos < 0:
+                continue
+            r = int(token_row[t])
+            pages = kv_indices[int(kv_indptr[r]) : int(kv_indptr[r + 1])].long()[: pos // page_size + 1]
+            assert (pages >= 0).all(), "a page the query sees was given back"
+            entries = k_pool[pages].permute(1, 0, 2, 3).reshape(kv_heads, -1, k_pool.shape[3])[:, : pos + 1].float()
+            keys = entries[..., :dim]
+            vals = entries[..., dim:] if v_pool is None else v_pool[pages].permute(1, 0, 2, 3).reshape(kv_heads, -1, vdim)[:, : pos + 1].float()
+            distance = (pos - torch.arange(pos + 1)).float()
+            for h in range(heads):
+                s = (keys[h // group] @ q[t, h].float()) * scale - slopes[h] * distance + head_bias[h]
+                o = torch.sigmoid(s) @ vals[h // group]
+                if gate_col is not None:
+                    o = o * torch.sigmoid(gate_rows[t, gate_col + h * vdim : gate_col + (h + 1) * vdim].float())
+                out[t, h * vdim : (h + 1) * vdim] = o.to(q.dtype)
+        return out
+
+    # ---- activations, gates, scaled sums
+    def xielu(self, x, a_pos, a_neg):
+        z = x.float()
+        zn = torch.clamp(z, max=0.0)
+        return torch.where(z > 0, a_pos * z * z + 0.5 * z, a_neg * (torch.expm1(zn) - zn) + 0.5 * zn).to(x.dtype)
+
+    def head_gate_mul_(self, x, g, col, heads):
+        T, V = x.shape
+        gate = torch.sigmoid(g[:, col : col + heads].float())
+        x.copy_((x.float().reshape(T, heads, V // heads) * gate[:, :, None]).reshape(T, V).to(x.dtype))
+        return x
+
+    def wide_rms_norm_gated(self, stream, w, eps, out_dtype, addend, gate, gate_bias, rows=None):
+        s = stream + addend.float() * torch.sigmoid(gate + gate_bias)
+        if rows is None:
+            stream.copy_(s)
+        else:
+            s = s[rows.long()]
+        if w is None:
+            return s.to(out_dtype)
+        return (s * torch.rsqrt((s * s).mean(-1, keepdim=True) + eps) * w).to(out_dtype)
+
+    def scale_(self, x, factor):
+        return x.mul_(factor)
 
     # ---- the selective scan
     def mamba1_scan(self, xc, dt, dbc, xz, dt_bias, a, d, state, q_indptr, slots, inner, N, R):
