@@ -3,7 +3,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers L] [--impl reference]
     python bench.py --sizes 0.6b|8b|32b          the same line at another model's layer sizes
     python bench.py --workload serving --sizes 0.6b [--requests 32] [--budget 512] [--new-tokens 256] [--max-prompt 2048]
-    python bench.py --workload designs [--design vamatar|lafanex|nomivik]      the other designs' models beside models of equal size
+    python bench.py --workload designs [--design vamatar|lafanex|nomivik|lovurax]      the other designs' models beside models of equal size
 
 Prints ONE JSON line. ``value`` is decoded tokens per second over K timed decode steps of ``--batch`` requests
 that each hold ``--context`` tokens, timed on the device with CUDA events; ``e2e`` is the same through the
@@ -521,6 +521,61 @@ def nomivik_main(args) -> int:
     return 0
 
 
+# Lovurax models at the same widths, depths and vocabularies: of every four layers a retention (heads of 64 keys and 128 values, as
+# wide in values as the model), two attentions with sigmoid weights (16 query heads over 4 key/value heads) and a latent attention
+# (a latent of 256 or 512 numbers); a feed-forward of 4 x width without a gate and a gate of width x width on every residual sum.
+# The Nomivik model beside each is the closest design the engine has (a 32-bit stream with root-mean-square norms, a matrix
+# recurrence a head with a state slot, a grouped attention over pages).
+def _lovurax_config(width, heads, dim, layers, vocab, rank, **_):
+    retention = {"type": "retention", "mixer": {"heads": width // 128, "dim": 64, "vdim": 128, "rot": {"dims": 64, "base": 10000.0},
+                                                "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(width // 128 - 1, 1)) for h in range(width // 128)]}}
+    attention = {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                                                "q_temp": {"coef": 0.2, "every": 512}}}
+    latent = {"type": "latent_attention", "mixer": {"heads": heads, "dim": dim, "vdim": dim, "kv_rank": rank, "scale": dim ** -0.5}}
+    dense = {"kind": "dense", "ff": 4 * width}
+    order = (retention, attention, attention, latent)
+    return {"architecture": "Lovurax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 1.0,
+            "layers": [dict(order[i % 4], mlp=dense) for i in range(layers)]}
+
+
+def lovurax_main(args) -> int:
+    """Prefill and decode throughput of Lovurax models beside Nomivik models (the closest design the engine has) of equal width,
+    depth and vocabulary, one JSON line."""
+    import torch
+
+    from roost_b200.config.lovurax import LovuraxConfig
+    from roost_b200.config.nomivik import NomivikConfig
+    pk, pk_src = peaks()
+    out = {}
+    for name in args.design_sizes.split(","):
+        s = dict(DESIGN_SIZES[name])
+        s["dim"] = 128 if s["width"] >= 2048 else 64
+        s["dense_ff"] = 3 * s["width"]
+        rec = {}
+        for which in ("lovurax", "nomivik"):
+            if which == "lovurax":
+                model, _ = build_from_config(LovuraxConfig, _lovurax_config(**s), torch.bfloat16)
+            else:
+                model, _ = build_from_config(NomivikConfig, _nomivik_config(**s), torch.bfloat16)
+            r = {"weight_gb": round(model.weight_bytes() / 1e9, 3)}
+            ms = timed_prefill(model, args.prefill_tokens)
+            r["prefill"] = {"tokens": args.prefill_tokens, "ms": round(ms, 3), "tokens_per_s": round(args.prefill_tokens / ms * 1e3)}
+            for batch in _ints(args.design_batches):
+                tps, ms, launches, _ = timed_decode(model, batch, args.design_context, args.steps, max(args.warmup, 3))
+                r[f"decode_b{batch}"] = {"context": args.design_context, "ms": round(ms, 4), "tokens_per_s": round(tps), "launches": launches[0] // args.steps,
+                                         "library_launches": launches[1] // args.steps}
+            rec[which] = r
+            del model
+            gc.collect()
+            torch.cuda.empty_cache()
+        rec["config"] = {k: s[k] for k in ("width", "heads", "dim", "layers", "vocab", "rank")}
+        out[name] = rec
+    print(json.dumps({"metric": "prefill and decode tokens/s of Lovurax models beside Nomivik models of equal width, depth and vocabulary",
+                      "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "impl": "ours", "peaks": pk_src,
+                      "data": "synthetic: seeded random weights, seeded random tokens; device-timed with CUDA events", "sizes": out}))
+    return 0
+
+
 def designs_main(args) -> int:
     """Prefill and decode throughput of Vamatar models beside Qwen3-shaped models of equal size, one JSON line."""
     import torch
@@ -528,6 +583,8 @@ def designs_main(args) -> int:
         return lafanex_main(args)
     if args.design == "nomivik":
         return nomivik_main(args)
+    if args.design == "lovurax":
+        return lovurax_main(args)
     pk, pk_src = peaks()
     out = {}
     for name in args.design_sizes.split(","):
@@ -576,9 +633,10 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="layers built (default: all the layers of --sizes)")
     ap.add_argument("--sizes", default="8b", choices=sorted(SIZES), help="whose layer sizes: Qwen3-0.6B, -8B (the headline) or -32B")
     ap.add_argument("--design-sizes", default="w1024,w2048", help="--workload designs: which of the Vamatar layer sizes to measure")
-    ap.add_argument("--design", default="vamatar", choices=["vamatar", "lafanex", "nomivik"],
+    ap.add_argument("--design", default="vamatar", choices=["vamatar", "lafanex", "nomivik", "lovurax"],
                     help="--workload designs: vamatar (beside Qwen3-shaped models), lafanex (beside Vamatar models of equal size) or "
-                         "nomivik (beside Lafanex models with dense feed-forwards of equal size)")
+                         "nomivik (beside Lafanex models with dense feed-forwards of equal size) or lovurax (beside Nomivik models of "
+                         "equal size)")
     ap.add_argument("--design-batches", default="1,8", help="--workload designs: decode batch sizes")
     ap.add_argument("--design-context", type=int, default=1024, help="--workload designs: keys every decoding request holds")
     ap.add_argument("--workload", default="decode", choices=["decode", "serving", "designs"],

@@ -467,6 +467,14 @@ int roost_sigmoid_attention(const void* q, void* out, float* part, const void* k
                             const int32_t* kv_indptr, const int32_t* kv_indices, int tokens, int heads, int kv_heads, int dim, int vdim,
                             int page_size, float scale, int splits, int tiles_per_split, int dtype, roost_stream_t stream);
 
+/* The same on the tensor cores (bfloat16; dim and vdim multiples of 16 up to 128, entry a multiple of 8), a block per (row, 64 query
+ * tokens, query head): for steps that bring prompt portions. q_indptr: the rows' token ranges (rows + 1 entries). */
+int roost_sigmoid_attention_mma_supported(int dim, int vdim, int entry);
+int roost_sigmoid_attention_mma(const void* q, void* out, const void* k_base, const void* v_base, int entry, const void* gate, int64_t ld_gate,
+                                const float* slopes, const float* head_bias, const int32_t* positions, const int32_t* q_indptr,
+                                const int32_t* kv_indptr, const int32_t* kv_indices, int tokens, int rows, int heads, int kv_heads, int dim, int vdim,
+                                int page_size, float scale, roost_stream_t stream);
+
 /* ---- activations.cu ---- */
 /* y = a_pos z^2 + z / 2 (z > 0), a_neg (exp(z) - 1 - z) + z / 2 (z <= 0). */
 int roost_xielu(const void* x, void* out, int64_t n, float a_pos, float a_neg, int dtype, roost_stream_t stream);

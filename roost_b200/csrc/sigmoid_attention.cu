@@ -261,3 +261,224 @@ extern "C" int roost_sigmoid_attention(const void* q, void* out, float* part, co
   });
   return check_launch("sigmoid_attention");
 }
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// The same attention on the tensor cores (bfloat16, mma.sync m16n8k16), for steps that bring prompt portions.
+//
+// One block of four warps per (row of the step, 64 of its query tokens, query head); a warp 16 query tokens. Key tiles of 64 keys
+// and their values are staged in shared memory as bfloat16; S = Q K^T in 32-bit accumulators; every score becomes its weight
+// sigmoid(s scale - slope (i - j) + bias) in 32-bit, a key after the query's position none; the weights enter P V as two bfloat16
+// operands, their rounding and what it left over (16 bits of the 32-bit weights), summed in 32-bit accumulators over all key tiles;
+// the output gate and the one rounding come last. Sizes: dim and vdim multiples of 16 up to 128.
+namespace roost {
+
+constexpr int kSmTile = 64;       // query tokens a block, keys a tile
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// (x, y) as two bfloat16 in one register, and what the rounding left over likewise
+__device__ __forceinline__ void split_pair(float x, float y, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+  const __nv_bfloat162 l = __floats2bfloat162_rn(x - __bfloat162float(h.x), y - __bfloat162float(h.y));
+  hi = *reinterpret_cast<const uint32_t*>(&h);
+  lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+
+// Which (row, tile of 64 tokens) the block `b` takes: rows in order, each with ceil(tokens / 64) tiles. False beyond the step's.
+__device__ __forceinline__ bool sigmoid_tile_of_block(const int32_t* __restrict__ q_indptr, int rows, int b, int& r, int& k) {
+  for (r = 0; r < rows; ++r) {
+    const int tiles = (q_indptr[r + 1] - q_indptr[r] + kSmTile - 1) / kSmTile;
+    if (b < tiles) {
+      k = b;
+      return true;
+    }
+    b -= tiles;
+  }
+  return false;
+}
+
+template <int DMAX, int VMAX>
+__global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                                                                   const __nv_bfloat16* __restrict__ k_base, const __nv_bfloat16* __restrict__ v_base,
+                                                                   int entry, const __nv_bfloat16* __restrict__ gate, int64_t ld_gate,
+                                                                   const float* __restrict__ slopes, const float* __restrict__ head_bias,
+                                                                   const int32_t* __restrict__ positions, const int32_t* __restrict__ q_indptr,
+                                                                   const int32_t* __restrict__ kv_indptr, const int32_t* __restrict__ kv_indices,
+                                                                   int rows, int heads, int kv_heads, int dim, int vdim, int page_size, float scale) {
+  extern __shared__ __align__(16) unsigned char sm_raw[];
+  const int ldq = dim + 8, ldv = vdim + 8;                    // padded rows: 16-byte aligned, ldmatrix without bank conflicts
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(sm_raw);      // [64][dim + 8]
+  __nv_bfloat16* Ks = Qs + kSmTile * ldq;                            // [64][dim + 8]
+  __nv_bfloat16* Vs = Ks + kSmTile * ldq;                            // [64][vdim + 8]
+  pdl_launch_dependents();
+  int r, tile;
+  if (!sigmoid_tile_of_block(q_indptr, rows, blockIdx.x, r, tile)) return;
+  const int h = blockIdx.y, g = h / (heads / kv_heads);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int t0 = q_indptr[r] + tile * kSmTile;
+  const int n_valid = min(kSmTile, q_indptr[r + 1] - t0);
+  const int p0 = positions[t0];
+  if (p0 < 0) return;                                          // a padding row
+  const int p_last = p0 + n_valid - 1;
+  const int32_t* pages = kv_indices + kv_indptr[r];
+  const float slope = slopes[h], bias = head_bias[h];
+  pdl_wait();
+  // the block's queries
+  const int qchunks = dim / 8;
+  for (int idx = tid; idx < kSmTile * qchunks; idx += 128) {
+    const int row = idx / qchunks, c = (idx % qchunks) * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < n_valid) v = *reinterpret_cast<const uint4*>(q + ((size_t)(t0 + row) * heads + h) * dim + c);
+    *reinterpret_cast<uint4*>(Qs + row * ldq + c) = v;
+  }
+  __syncthreads();
+  uint32_t qa[DMAX / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < DMAX / 16; ++ks)
+    if (ks * 16 < dim) ldmatrix_x4(qa[ks], Qs + (warp * 16 + (lane & 15)) * ldq + ks * 16 + (lane >> 4) * 8);
+  float o[VMAX / 8][4];
+#pragma unroll
+  for (int n = 0; n < VMAX / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  const int row_lo = warp * 16 + (lane >> 2);                 // the thread's two query rows within the tile: row_lo and row_lo + 8
+  const int pos_lo = p0 + row_lo, pos_hi = pos_lo + 8;
+  const int vchunks = vdim / 8;
+  const int n_tiles = p_last / kSmTile + 1;
+  for (int kt = 0; kt < n_tiles; ++kt) {
+    const int k0 = kt * kSmTile;
+    __syncthreads();                                           // everybody is done with the tile before
+    for (int idx = tid; idx < kSmTile * qchunks; idx += 128) {
+      const int key = idx / qchunks, c = (idx % qchunks) * 8;
+      const int kp = k0 + key;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (kp <= p_last) v = *reinterpret_cast<const uint4*>(k_base + (((size_t)pages[kp / page_size] * kv_heads + g) * page_size + kp % page_size) * entry + c);
+      *reinterpret_cast<uint4*>(Ks + key * ldq + c) = v;
+    }
+    for (int idx = tid; idx < kSmTile * vchunks; idx += 128) {
+      const int key = idx / vchunks, c = (idx % vchunks) * 8;
+      const int kp = k0 + key;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (kp <= p_last) v = *reinterpret_cast<const uint4*>(v_base + (((size_t)pages[kp / page_size] * kv_heads + g) * page_size + kp % page_size) * entry + c);
+      *reinterpret_cast<uint4*>(Vs + key * ldv + c) = v;
+    }
+    __syncthreads();
+    if (k0 > p0 + warp * 16 + 15) continue;                    // every key of the tile lies after the warp's last query
+    // S = Q K^T: 16 queries x 64 keys a warp
+    float s[kSmTile / 8][4];
+#pragma unroll
+    for (int n = 0; n < kSmTile / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < DMAX / 16; ++ks) {
+      if (ks * 16 < dim) {
+#pragma unroll
+        for (int np = 0; np < kSmTile / 16; ++np) {
+          uint32_t b[4];
+          ldmatrix_x4(b, Ks + (np * 16 + (lane & 7) + (lane >> 4) * 8) * ldq + ks * 16 + ((lane >> 3) & 1) * 8);
+          mma_bf16(s[2 * np], qa[ks], b[0], b[1]);
+          mma_bf16(s[2 * np + 1], qa[ks], b[2], b[3]);
+        }
+      }
+    }
+    // the weights, then P V with P as two operands
+#pragma unroll
+    for (int kk = 0; kk < kSmTile / 16; ++kk) {
+      uint32_t hi[4], lo[4];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int n = 2 * kk + half;
+        const int j = k0 + n * 8 + (lane & 3) * 2;
+        float w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int pos = e < 2 ? pos_lo : pos_hi, jj = j + (e & 1);
+          const float z = fmaf(s[n][e], scale, bias) - slope * (float)(pos - jj);
+          w[e] = jj <= pos ? 1.0f / (1.0f + __expf(-z)) : 0.f;
+        }
+        split_pair(w[0], w[1], hi[2 * half], lo[2 * half]);
+        split_pair(w[2], w[3], hi[2 * half + 1], lo[2 * half + 1]);
+      }
+      // A fragment order: (rows g, keys 0-7), (rows g + 8, keys 0-7), (rows g, keys 8-15), (rows g + 8, keys 8-15)
+      const uint32_t ah[4] = {hi[0], hi[1], hi[2], hi[3]}, al[4] = {lo[0], lo[1], lo[2], lo[3]};
+#pragma unroll
+      for (int np = 0; np < VMAX / 16; ++np) {
+        if (np * 16 < vdim) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv + np * 16 + (lane >> 4) * 8);
+          mma_bf16(o[2 * np], ah, b[0], b[1]);
+          mma_bf16(o[2 * np], al, b[0], b[1]);
+          mma_bf16(o[2 * np + 1], ah, b[2], b[3]);
+          mma_bf16(o[2 * np + 1], al, b[2], b[3]);
+        }
+      }
+    }
+  }
+  // the output gate and the one rounding
+#pragma unroll
+  for (int n = 0; n < VMAX / 8; ++n) {
+    if (n * 8 < vdim) {
+      const int c = n * 8 + (lane & 3) * 2;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int row = row_lo + half * 8;
+        if (row < n_valid) {
+          const size_t t = (size_t)(t0 + row);
+          float x = o[n][2 * half], y = o[n][2 * half + 1];
+          if (gate != nullptr) {
+            const __nv_bfloat162 gv = *reinterpret_cast<const __nv_bfloat162*>(gate + t * ld_gate + (size_t)h * vdim + c);
+            x *= 1.0f / (1.0f + __expf(-__bfloat162float(gv.x)));
+            y *= 1.0f / (1.0f + __expf(-__bfloat162float(gv.y)));
+          }
+          *reinterpret_cast<__nv_bfloat162*>(out + (t * heads + h) * vdim + c) = __floats2bfloat162_rn(x, y);
+        }
+      }
+    }
+  }
+}
+
+}  // namespace roost
+
+extern "C" int roost_sigmoid_attention_mma_supported(int dim, int vdim, int entry) {
+  return dim % 16 == 0 && vdim % 16 == 0 && dim <= 128 && vdim <= 128 && entry % 8 == 0;
+}
+
+// q [tokens, heads, dim], out [tokens, heads * vdim], both bfloat16; rows: the step's rows (q_indptr has rows + 1 entries).
+extern "C" int roost_sigmoid_attention_mma(const void* q, void* out, const void* k_base, const void* v_base, int entry, const void* gate, int64_t ld_gate,
+                                           const float* slopes, const float* head_bias, const int32_t* positions, const int32_t* q_indptr,
+                                           const int32_t* kv_indptr, const int32_t* kv_indices, int tokens, int rows, int heads, int kv_heads, int dim,
+                                           int vdim, int page_size, float scale, roost_stream_t stream) {
+  ROOST_REQUIRE(tokens >= 0 && rows >= 0 && heads > 0 && kv_heads > 0 && page_size > 0 && heads % kv_heads == 0, "sigmoid_attention_mma: sizes must be positive");
+  ROOST_REQUIRE(q && out && k_base && v_base && slopes && head_bias && positions && q_indptr && kv_indptr && kv_indices,
+                "sigmoid_attention_mma: a pointer is null");
+  if (!roost_sigmoid_attention_mma_supported(dim, vdim, entry)) return fail(ROOST_ERR_UNSUPPORTED, "sigmoid_attention_mma: sizes no tensor-core form serves");
+  ROOST_REQUIRE((uintptr_t)q % 16 == 0 && (uintptr_t)k_base % 16 == 0 && (uintptr_t)v_base % 16 == 0 && (uintptr_t)out % 4 == 0 &&
+                    (gate == nullptr || ((uintptr_t)gate % 4 == 0 && ld_gate % 2 == 0 && ld_gate >= (int64_t)heads * vdim)),
+                "sigmoid_attention_mma: a pointer is not aligned");
+  if (tokens == 0 || rows == 0) return ROOST_OK;
+  if (heads > 65535) return fail(ROOST_ERR_UNSUPPORTED, "sigmoid_attention_mma: too many heads");
+  const size_t smem = ((size_t)2 * kSmTile * (dim + 8) + (size_t)kSmTile * (vdim + 8)) * sizeof(__nv_bfloat16);
+  dim3 grid((tokens + kSmTile - 1) / kSmTile + rows, heads);
+#define ROOST_SG_MMA(DMAX, VMAX)                                                                                                                  \
+  do {                                                                                                                                            \
+    auto kernel = sigmoid_attention_mma_kernel<DMAX, VMAX>;                                                                                       \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                                   \
+    launch_kernel(kernel, grid, dim3(128), smem, (cudaStream_t)stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_base, \
+                  (const __nv_bfloat16*)v_base, entry, (const __nv_bfloat16*)gate, ld_gate, slopes, head_bias, positions, q_indptr, kv_indptr,    \
+                  kv_indices, rows, heads, kv_heads, dim, vdim, page_size, scale);                                                                \
+  } while (0)
+  if (dim <= 64 && vdim <= 64) ROOST_SG_MMA(64, 64);
+  else if (dim <= 64) ROOST_SG_MMA(64, 128);
+  else if (vdim <= 64) ROOST_SG_MMA(128, 64);
+  else ROOST_SG_MMA(128, 128);
+#undef ROOST_SG_MMA
+  return check_launch("sigmoid_attention_mma");
+}

@@ -166,6 +166,9 @@ _SIGNATURES = {
                                         c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_void_p],
     "roost_sigmoid_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
+    "roost_sigmoid_attention_mma_supported": [c_int, c_int, c_int],
+    "roost_sigmoid_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "roost_xielu": [c_void_p, c_void_p, c_int64, c_float, c_float, c_int, c_void_p],
     "roost_head_gate_mul": [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "roost_wide_rms_norm_gated": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
@@ -1114,10 +1117,17 @@ class KernelLibrary:
                    dtype_code(qkv.dtype), _stream())
         return q
 
+    SIGMOID_MMA_MIN_TOKENS = 32     # tokens from which a bfloat16 step that brings prompt portions runs the tensor-core form
+
+    def sigmoid_attention_mma_supported(self, dim: int, vdim: int, two_planes: bool) -> bool:
+        return bool(self._lib.roost_sigmoid_attention_mma_supported(int(dim), int(vdim), int(dim if two_planes else dim + vdim)))
+
     def sigmoid_attention(self, q, k_pool, v_pool, gate_rows, gate_col, slopes, head_bias, positions, token_row, kv_indptr, kv_indices, kv_heads, vdim,
-                          scale, kv_cap: int = 0) -> torch.Tensor:
+                          scale, kv_cap: int = 0, q_indptr: torch.Tensor | None = None) -> torch.Tensor:
         """out[t, h] = sum over visible keys j of sigmoid((q . k_j) scale - slopes[h] (p - j) + head_bias[h]) v_j, times
-        sigmoid(gate_rows[t, gate_col + h * vdim : ...]) when ``gate_col`` is not None: [T, heads * vdim]."""
+        sigmoid(gate_rows[t, gate_col + h * vdim : ...]) when ``gate_col`` is not None: [T, heads * vdim]. With ``q_indptr`` (the rows'
+        token ranges) a bfloat16 step runs on the tensor cores where the sizes allow; without, the 32-bit form, a token's keys dealt to
+        several blocks when the step alone would not fill the device."""
         _need(q, "q"); _need(k_pool, "k_pool", q.dtype); _need(slopes, "slopes", torch.float32); _need(head_bias, "head_bias", torch.float32)
         for n, t in (("positions", positions), ("token_row", token_row), ("kv_indptr", kv_indptr), ("kv_indices", kv_indices)):
             _need(t, n, torch.int32)
@@ -1132,6 +1142,12 @@ class KernelLibrary:
             gate_ptr, ld_gate = gate_rows.data_ptr() + gate_col * gate_rows.element_size(), gate_rows.stride(0)
         kb, vb, entry = self._sink_cache(k_pool, v_pool, dim, vdim)
         out = torch.empty((T, heads * vdim), dtype=q.dtype, device=q.device)
+        if q_indptr is not None and q.dtype == torch.bfloat16 and self.sigmoid_attention_mma_supported(dim, vdim, v_pool is not None):
+            _need(q_indptr, "q_indptr", torch.int32)
+            self._call("roost_sigmoid_attention_mma", _ptr(q), _ptr(out), kb, vb, entry, gate_ptr, ld_gate, _ptr(slopes), _ptr(head_bias), _ptr(positions),
+                       _ptr(q_indptr), _ptr(kv_indptr), _ptr(kv_indices), T, q_indptr.numel() - 1, heads, kv_heads, dim, vdim, k_pool.shape[2],
+                       float(scale), _stream())
+            return out
         gy = kv_heads * (-(-(heads // kv_heads) // 8))
         splits, per = self.sink_splits_for(T, gy, kv_cap) if kv_cap else (1, 1 << 24)
         part = torch.empty((T * heads * splits * vdim,), dtype=torch.float32, device=q.device) if splits > 1 else None

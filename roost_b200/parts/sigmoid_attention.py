@@ -5,7 +5,9 @@ its root mean square and multiplies by the queries' or the keys' weight, multipl
 position, 1 + c ln(floor((p + 1) / every) + 1), writes them to a tensor of their own and the keys and values into the step's
 page slots; attention of the step's queries over the pages, key j of query i weighing sigmoid((q_i . k_j) scale - slope_h (i - j)
 + b_h), the weighted sum of the values multiplied by sigmoid(gate) in the same kernel; the output projection. Scores, weights and
-sums are 32-bit. A step of few rows deals a token's keys to several blocks whose partial sums a second kernel adds in order.
+sums are 32-bit. A step of few rows deals a token's keys to several blocks whose partial sums a second kernel adds in order; a
+bfloat16 step that brings prompt portions runs the same sums on the tensor cores (mma.sync), the 32-bit weights entering P V as two
+bfloat16 operands.
 
 The cache is a paged group: two planes (keys, values) when keys and values have one size, else one plane whose entries are
 [key | value] of one key/value head.
@@ -79,8 +81,12 @@ class SigmoidAttention(Mixer):
         q = k.sigmoid_attention_prepare(qkv, cache.k_pool, cache.v_pool, self.q_weight, self.k_weight, batch.positions, tables.slot_mapping,
                                         s.num_heads, s.num_kv_heads, s.head_dim, s.v_dim, s.qk_norm_eps, s.temp_coef, s.temp_every, cache.page_size)
         gate_col = self.q_width + self.k_width + self.v_width if s.output_gate else None
+        # steps that bring prompt portions run on the tensor cores in bfloat16 where the sizes allow (a function of the step's size
+        # and kind only, so a captured step keeps its way); steps that decode, float32 and other sizes run the 32-bit kernel
+        portions = not batch.all_single and batch.num_tokens >= getattr(k, "SIGMOID_MMA_MIN_TOKENS", 1 << 30)
         o = k.sigmoid_attention(q, cache.k_pool, cache.v_pool, qkv, gate_col, self.slopes, self.head_bias, batch.positions, batch.token_row,
-                                tables.kv_indptr, tables.kv_indices, s.num_kv_heads, s.v_dim, s.scale, kv_cap=batch.kv_cap)
+                                tables.kv_indptr, tables.kv_indices, s.num_kv_heads, s.v_dim, s.scale, kv_cap=batch.kv_cap,
+                                **({"q_indptr": batch.q_indptr} if portions else {}))
         return self.out(o)
 
 
