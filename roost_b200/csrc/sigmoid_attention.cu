@@ -390,6 +390,7 @@ __global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const __nv_b
       }
     }
     // the weights, then P V with P as two operands
+    const bool diagonal = k0 + kSmTile - 1 > p0 + warp * 16;
 #pragma unroll
     for (int kk = 0; kk < kSmTile / 16; ++kk) {
       uint32_t hi[4], lo[4];
@@ -397,12 +398,18 @@ __global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const __nv_b
       for (int half = 0; half < 2; ++half) {
         const int n = 2 * kk + half;
         const int j = k0 + n * 8 + (lane & 3) * 2;
+        // bias - slope (i - j) for the thread's two rows at key j; the key after it adds one slope
+        const float b_lo = fmaf(slope, (float)(j - pos_lo), bias), b_hi = fmaf(slope, (float)(j - pos_hi), bias);
         float w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int pos = e < 2 ? pos_lo : pos_hi, jj = j + (e & 1);
-          const float z = fmaf(s[n][e], scale, bias) - slope * (float)(pos - jj);
-          w[e] = jj <= pos ? 1.0f / (1.0f + __expf(-z)) : 0.f;
+        w[0] = __fdividef(1.0f, 1.0f + __expf(-fmaf(s[n][0], scale, b_lo)));
+        w[1] = __fdividef(1.0f, 1.0f + __expf(-fmaf(s[n][1], scale, b_lo + slope)));
+        w[2] = __fdividef(1.0f, 1.0f + __expf(-fmaf(s[n][2], scale, b_hi)));
+        w[3] = __fdividef(1.0f, 1.0f + __expf(-fmaf(s[n][3], scale, b_hi + slope)));
+        if (diagonal) {                                          // only the tiles around the warp's own positions hold keys to hide
+          if (j > pos_lo) w[0] = 0.f;
+          if (j + 1 > pos_lo) w[1] = 0.f;
+          if (j > pos_hi) w[2] = 0.f;
+          if (j + 1 > pos_hi) w[3] = 0.f;
         }
         split_pair(w[0], w[1], hi[2 * half], lo[2 * half]);
         split_pair(w[2], w[3], hi[2 * half + 1], lo[2 * half + 1]);

@@ -88,7 +88,7 @@ def tensor_shapes(cfg) -> dict:
     return shapes
 
 
-def draw_tensors(cfg, seed: int, std: float = 0.25) -> dict:
+def draw_tensors(cfg, seed: int, std: float = 0.12) -> dict:
     g = torch.Generator().manual_seed(seed)
     out = {}
     for name, shape in tensor_shapes(cfg).items():
