@@ -3,10 +3,10 @@
 Lovurax is a pre-norm decoder over a 32-bit residual stream with root-mean-square norms, a gate on every residual sum and logits
 against the embedding table times ``logit_scale``. ``layers`` lists its layers: each names its mixer by ``type`` with the mixer's
 sizes under ``mixer`` and its feed-forward under ``mlp`` (``dense``: W_down act(W_up h) with the xIELU activation; null: none).
-Mixers: ``retention`` (linear attention with a fixed ``decay`` a head, q and k rotated in split halves over ``rot.dims`` elements),
+Mixers: ``retention`` (a matrix state a head that fades by its ``decay`` a token, q and k rotated in split halves over ``rot.dims`` elements),
 ``attention`` (grouped heads, normed queries and keys, a query temperature ``q_temp`` that grows with the position, a bias that
-grows with the distance, sigmoid weights that are not normalized, a bias a head, an output gate) and ``latent_attention`` (keys and
-values made from one cached latent vector of ``kv_rank`` numbers a token, no positions, a softmax, a gate a head). Every sublayer's
+grows with the distance, a sigmoid of each score as that key's weight, a bias a head, an output gate) and ``latent_attention`` (keys and
+values made from one cached latent vector of ``kv_rank`` numbers a token, nothing that depends on the position, a softmax, a gate a head). Every sublayer's
 output is multiplied by sigmoid(W h + b) of the sublayer's own input before it joins the stream. Tensor names: ``embed``,
 ``l<i>.norm1`` / ``.norm2``, ``l<i>.mix.*``, ``l<i>.mlp.*``, ``l<i>.rg1`` / ``.rg2`` with ``.b``, ``final.norm``. No size and no
 constant that config.json gives stands in code.

@@ -172,7 +172,8 @@ class MatrixMemorySpec(MixerSpec):
 
 @dataclass(frozen=True)
 class RetentionSpec(MixerSpec):
-    """Linear attention with a fixed decay a head, no softmax and no denominator. q = W_q h, k = W_k h (``num_heads`` x ``head_dim``),
+    """A matrix state a head that fades by a constant factor a token and is read by the query as it is: nothing is exponentiated and
+    nothing divides. q = W_q h, k = W_k h (``num_heads`` x ``head_dim``),
     v = W_v h (``num_heads`` x ``v_dim``); q and k are rotated (``position``), k then multiplied by head_dim^(-1/2); per head
     S <- decay_h S + k v^T from S = 0, o = S^T q. Each head's o is divided by its root mean square (``eps``, no weight); the heads side
     by side are multiplied by silu(W_g h) and projected out. S is kept per request in 32-bit."""
@@ -189,7 +190,7 @@ class RetentionSpec(MixerSpec):
 @dataclass(frozen=True)
 class SigmoidAttentionSpec(MixerSpec):
     """Grouped-query causal attention without a softmax: a visible key j gets the weight sigmoid(s_ij + b_h) of its own, and the
-    weights are not normalized over the keys. Queries and keys are divided by their root mean square over the head (``qk_norm_eps``)
+    weights are used as they are: nothing divides by their sum. Queries and keys are divided by their root mean square over the head (``qk_norm_eps``)
     and multiplied by a weight of ``head_dim`` numbers shared by the heads (one for queries, one for keys). ``temp_coef`` c > 0: the
     query at position p is multiplied by 1 + c ln(floor((p + 1) / ``temp_every``) + 1). s_ij = (q_i . k_j) ``scale`` - slope_h (i - j)
     with one ``slopes`` entry a query head (empty: no distance bias); b_h is a stored number a head (``head_bias``). With

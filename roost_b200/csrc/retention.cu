@@ -1,4 +1,4 @@
-// Retention: linear attention with a fixed decay a head, no softmax and no denominator, in 32-bit arithmetic.
+// Retention: a matrix state a head that fades by a constant factor a token and is read by the query as it is, in 32-bit arithmetic.
 //
 // Per (row, head), for the row's tokens in order, with q, k (dim numbers) and v (vdim numbers):
 //   S <- decay_h S + k v^T,   o = S^T q.

@@ -1,5 +1,5 @@
 // Grouped-query causal attention without a softmax: the weight of a visible key is the sigmoid of its score, and the weights
-// are not normalized over the keys. In 32-bit arithmetic over a paged cache of either dtype.
+// are used as they are (nothing divides by their sum). In 32-bit arithmetic over a paged cache of either dtype.
 //
 //   prepare:   per token, on a row [q heads | k heads | v heads | ...] of the fused projection: every query and key head is
 //              divided by sqrt(mean(x^2) + eps) and multiplied by a weight of dim numbers (one for the queries, one for the keys,
@@ -266,7 +266,7 @@ extern "C" int roost_sigmoid_attention(const void* q, void* out, float* part, co
 // The same attention on the tensor cores (bfloat16, mma.sync m16n8k16), for steps that bring prompt portions.
 //
 // One block of four warps per (row of the step, 64 of its query tokens, query head); a warp 16 query tokens. Key tiles of 64 keys
-// and their values are staged in shared memory as bfloat16; S = Q K^T in 32-bit accumulators; every score becomes its weight
+// and their values are staged in shared memory as bfloat16 by asynchronous copies, one tile ahead; S = Q K^T in 32-bit accumulators; every score becomes its weight
 // sigmoid(s scale - slope (i - j) + bias) in 32-bit, a key after the query's position none; the weights enter P V as two bfloat16
 // operands, their rounding and what it left over (16 bits of the 32-bit weights), summed in 32-bit accumulators over all key tiles;
 // the output gate and the one rounding come last. Sizes: dim and vdim multiples of 16 up to 128.
@@ -319,11 +319,12 @@ __global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const __nv_b
   extern __shared__ __align__(16) unsigned char sm_raw[];
   const int ldq = dim + 8, ldv = vdim + 8;                    // padded rows: 16-byte aligned, ldmatrix without bank conflicts
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(sm_raw);      // [64][dim + 8]
-  __nv_bfloat16* Ks = Qs + kSmTile * ldq;                            // [64][dim + 8]
-  __nv_bfloat16* Vs = Ks + kSmTile * ldq;                            // [64][vdim + 8]
+  __nv_bfloat16* Kb = Qs + kSmTile * ldq;                            // two buffers of [64][dim + 8]
+  __nv_bfloat16* Vb = Kb + 2 * kSmTile * ldq;                        // two buffers of [64][vdim + 8]
   pdl_launch_dependents();
   int r, tile;
-  if (!sigmoid_tile_of_block(q_indptr, rows, blockIdx.x, r, tile)) return;
+  // the blocks with the most keys ahead of them (a row's last tiles) start first
+  if (!sigmoid_tile_of_block(q_indptr, rows, (int)gridDim.x - 1 - (int)blockIdx.x, r, tile)) return;
   const int h = blockIdx.y, g = h / (heads / kv_heads);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int t0 = q_indptr[r] + tile * kSmTile;
@@ -354,25 +355,38 @@ __global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const __nv_b
   const int pos_lo = p0 + row_lo, pos_hi = pos_lo + 8;
   const int vchunks = vdim / 8;
   const int n_tiles = p_last / kSmTile + 1;
+  // a tile's keys and values come by asynchronous 16-byte copies (a key after the block's last query: zeros), one tile ahead
+  auto fetch = [&](int kt) {
+    const int k0 = kt * kSmTile;
+    __nv_bfloat16* Kd = Kb + (kt & 1) * kSmTile * ldq;
+    __nv_bfloat16* Vd = Vb + (kt & 1) * kSmTile * ldv;
+    for (int idx = tid; idx < kSmTile * (qchunks + vchunks); idx += 128) {
+      const bool is_k = idx < kSmTile * qchunks;
+      const int i2 = is_k ? idx : idx - kSmTile * qchunks;
+      const int per = is_k ? qchunks : vchunks;
+      const int key = i2 / per, c = (i2 % per) * 8;
+      const int kp = min(k0 + key, p_last);
+      const size_t at = (((size_t)pages[kp / page_size] * kv_heads + g) * page_size + kp % page_size) * entry + c;
+      const __nv_bfloat16* src = (is_k ? k_base : v_base) + at;
+      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(is_k ? Kd + key * ldq + c : Vd + key * ldv + c);
+      const int bytes = k0 + key <= p_last ? 16 : 0;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+  fetch(0);
   for (int kt = 0; kt < n_tiles; ++kt) {
     const int k0 = kt * kSmTile;
-    __syncthreads();                                           // everybody is done with the tile before
-    for (int idx = tid; idx < kSmTile * qchunks; idx += 128) {
-      const int key = idx / qchunks, c = (idx % qchunks) * 8;
-      const int kp = k0 + key;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (kp <= p_last) v = *reinterpret_cast<const uint4*>(k_base + (((size_t)pages[kp / page_size] * kv_heads + g) * page_size + kp % page_size) * entry + c);
-      *reinterpret_cast<uint4*>(Ks + key * ldq + c) = v;
-    }
-    for (int idx = tid; idx < kSmTile * vchunks; idx += 128) {
-      const int key = idx / vchunks, c = (idx % vchunks) * 8;
-      const int kp = k0 + key;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (kp <= p_last) v = *reinterpret_cast<const uint4*>(v_base + (((size_t)pages[kp / page_size] * kv_heads + g) * page_size + kp % page_size) * entry + c);
-      *reinterpret_cast<uint4*>(Vs + key * ldv + c) = v;
+    const __nv_bfloat16* Ks = Kb + (kt & 1) * kSmTile * ldq;
+    const __nv_bfloat16* Vs = Vb + (kt & 1) * kSmTile * ldv;
+    if (kt + 1 < n_tiles) {
+      fetch(kt + 1);
+      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     }
     __syncthreads();
-    if (k0 > p0 + warp * 16 + 15) continue;                    // every key of the tile lies after the warp's last query
+    if (k0 <= p0 + warp * 16 + 15) {                            // else every key of the tile lies after the warp's last query
     // S = Q K^T: 16 queries x 64 keys a warp
     float s[kSmTile / 8][4];
 #pragma unroll
@@ -428,6 +442,8 @@ __global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const __nv_b
         }
       }
     }
+    }
+    __syncthreads();                                           // everybody is done with the buffer the next fetch fills
   }
   // the output gate and the one rounding
 #pragma unroll
@@ -472,7 +488,7 @@ extern "C" int roost_sigmoid_attention_mma(const void* q, void* out, const void*
                 "sigmoid_attention_mma: a pointer is not aligned");
   if (tokens == 0 || rows == 0) return ROOST_OK;
   if (heads > 65535) return fail(ROOST_ERR_UNSUPPORTED, "sigmoid_attention_mma: too many heads");
-  const size_t smem = ((size_t)2 * kSmTile * (dim + 8) + (size_t)kSmTile * (vdim + 8)) * sizeof(__nv_bfloat16);
+  const size_t smem = ((size_t)3 * kSmTile * (dim + 8) + (size_t)2 * kSmTile * (vdim + 8)) * sizeof(__nv_bfloat16);
   dim3 grid((tokens + kSmTile - 1) / kSmTile + rows, heads);
 #define ROOST_SG_MMA(DMAX, VMAX)                                                                                                                  \
   do {                                                                                                                                            \

@@ -1,4 +1,4 @@
-"""Retention: linear attention with a fixed decay a head, as a mixer with a fixed-size state per request.
+"""Retention: a matrix state a head that fades by a constant factor a token, as a mixer with a fixed-size state per request.
 
 Per step: one projection gives a token's [q | k | v | g] (g: the output gate's argument, ``heads`` x ``v_dim`` wide); one kernel
 turns the first ``rotary_dim`` elements of every query and key head in pairs (i, i + rotary_dim / 2) by position x frequency

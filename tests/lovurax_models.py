@@ -97,7 +97,7 @@ def draw_tensors(cfg, seed: int, std: float = 0.12) -> dict:
         if "norm" in name:
             t = 1.0 + 0.1 * r
         elif name.endswith(".pb"):
-            t = -4.0 + 0.7 * r                      # a key counts little unless its score is large: the weights are not normalized
+            t = -4.0 + 0.7 * r                      # a key counts little unless its score is large: nothing divides the weights by their sum
         elif name.endswith(".act"):
             t = -0.5 + 0.8 * r
         elif name.endswith("mlp.up"):

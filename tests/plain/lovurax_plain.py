@@ -3,7 +3,7 @@ formula has them. It shares no code with the package and is what the engine's re
 
 Layers are pre-norm: x <- x + gate1 * mixer(n1), x <- x + gate2 * ff(n2) with n = rms_norm(x) and gate = sigmoid(W n + b).
 Mixers: ``retention`` (a decaying sum of k v^T a head, rotated q and k), ``attention`` (grouped heads, normed q and k, a query
-temperature that grows with the position, a bias that grows with the distance, sigmoid weights that are not normalized, an
+temperature that grows with the position, a bias that grows with the distance, a sigmoid of every score as its key's weight, an
 output gate) and ``latent_attention`` (keys and values made from one cached latent vector a token, softmax, a gate a head).
 """
 from __future__ import annotations

@@ -336,7 +336,7 @@ FAR = {
 
 
 def sharpened(tmp_path_factory, kind):
-    # the attention's weights are not normalized: hundreds of other keys add their values too, so the key's own is made larger
+    # nothing divides the attention's weights by their sum: hundreds of other keys add their values too, so the key's own is made larger
     value = 24.0 if kind == "attention" else 6.0
 
     def change(c, t):
@@ -508,3 +508,69 @@ def test_a_missing_or_misshapen_tensor_is_named(tmp_path):
     with pytest.raises(WeightError) as e:
         H.make_model(folder, torch.float32, "fake")
     assert "l0.mix.pb" in e.value.missing and any(n == "l0.rg1.b" for n, _, _ in e.value.wrong_shape)
+
+
+# ------------------------------------------------------------------------------------------------ the programs a user runs
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_replay_program_on_a_lovurax_model(tmp_path_factory, tmp_path, dtype):
+    """bin/trace_run as a subprocess: the model class found by config.json, three requests through a pool of 192 tokens (the third
+    takes the pages and the slot the first gave back), portions beside single tokens, a request that sits out a step."""
+    from tests.test_trace_run_gpu import TraceRun
+    folder, cfg, weights = model_dir(tmp_path_factory, "mixed", LM.MIXED, seed=5)
+    a, b, c = ids_for(cfg, 70, 21), ids_for(cfg, 45, 22), ids_for(cfg, 100, 23)
+    want = {k: P.forward(cfg, weights, ids) for k, ids in (("a", a), ("b", b), ("c", c))}
+    run = TraceRun(folder, dtype, tmp_path, max_tokens=192)
+    try:
+        got_a = [run.step([("a", a[:38], list(range(38)))])]
+        out = run.step([("b", b[:2], [0, 1]), ("a", a[38:40], [0, 1])])
+        got_b = [out[:2]]
+        got_a.append(out[2:])
+        assert run.step([("b", b[2:30], [])]) is None
+        out = run.step([("a", a[40:41], [0]), ("b", b[30:45], list(range(15)))], end=["b"])
+        got_a.append(out[:1])
+        got_b.append(out[1:])
+        for i in range(41, 70):
+            got_a.append(run.step([("a", a[i : i + 1], [0])], end=["a"] if i == 69 else []))
+        got_c = run.step([("c", c, list(range(100)))], end=["c"])
+    finally:
+        run.close()
+    bound = F32_TOKEN if dtype == "float32" else BF16_TOKEN
+    for what, got, ref in (("a", torch.cat(got_a), want["a"]), ("b, first two", got_b[0], want["b"][:2]), ("b, last portion", got_b[1], want["b"][30:]),
+                           ("c", got_c, want["c"])):
+        errs = position_errors(got, ref)
+        print(f"MEASURED replay {what} {dtype}: worst position's error {float(errs.max()):.3e}")
+        assert float(errs.max()) < bound, (what, float(errs.max()))
+
+
+@pytest.mark.gpu
+def test_the_command_line_generates_from_a_lovurax_model(tmp_path_factory):
+    import json
+    import subprocess
+    import sys
+
+    from tests.conftest import ROOT
+    folder, cfg, weights = model_dir(tmp_path_factory, "odd", LM.ODD, seed=len("odd"))
+    prompt = ids_for(cfg, 12, 3)
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "roost"), "generate", "--model", str(folder), "--dtype", "float32", "--prompt-ids",
+                        ",".join(map(str, prompt)), "--max-output-tokens", "8", "--ignore-eos", "--attention-blocks", "8", "--max-sequences", "2"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    assert out["finish_reason"] == "length" and out["prompt_tokens"] == 12 and len(out["token_ids"]) == 8
+    logits = P.forward(cfg, weights, list(prompt) + out["token_ids"][:-1])
+    for j, tok in enumerate(out["token_ids"]):
+        top = logits[len(prompt) - 1 + j].topk(2)
+        if float(top.values[0] - top.values[1]) > 1e-3:
+            assert tok == int(top.indices[0]), (j, tok, int(top.indices[0]))
+
+
+def test_random_weights_for_a_lovurax_configuration_load_and_run(tmp_path):
+    """The random-weights mode writes a folder from the configuration alone (every parameter's shape and role comes from the parts'
+    declarations); the loader reads it back and a step runs."""
+    from roost_b200.weights.random_init import write_random_model
+    write_random_model(tmp_path / "m", LM.MIXED, seed=3, std=0.05)
+    model = H.make_model(tmp_path / "m", torch.float32, "fake")
+    ex = StepExecutor(model, page_size=4, num_pages=16, max_requests=2)
+    out = ex.step([StepEntry("a", [1, 2, 3], [2])])
+    assert out.shape == (1, LM.MIXED["vocab"]) and bool(torch.isfinite(out).all())
