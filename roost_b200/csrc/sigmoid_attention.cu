@@ -269,7 +269,9 @@ extern "C" int roost_sigmoid_attention(const void* q, void* out, float* part, co
 // and their values are staged in shared memory as bfloat16 by asynchronous copies, one tile ahead; S = Q K^T in 32-bit accumulators; every score becomes its weight
 // sigmoid(s scale - slope (i - j) + bias) in 32-bit, a key after the query's position none; the weights enter P V as two bfloat16
 // operands, their rounding and what it left over (16 bits of the 32-bit weights), summed in 32-bit accumulators over all key tiles;
-// the output gate and the one rounding come last. Sizes: dim and vdim multiples of 16 up to 128.
+// the output gate and the one rounding come last. A tile of queries far into a long row has its keys dealt to several blocks in
+// chunks of tiles_a_chunk key tiles (the sums are plain sums: a second kernel adds the chunks' in order), so that the blocks of a
+// row's last tiles do not run many times as long as those of its first. Sizes: dim and vdim multiples of 16 up to 128.
 namespace roost {
 
 constexpr int kSmTile = 64;       // query tokens a block, keys a tile
@@ -315,7 +317,8 @@ __global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const __nv_b
                                                                    const float* __restrict__ slopes, const float* __restrict__ head_bias,
                                                                    const int32_t* __restrict__ positions, const int32_t* __restrict__ q_indptr,
                                                                    const int32_t* __restrict__ kv_indptr, const int32_t* __restrict__ kv_indices,
-                                                                   int rows, int heads, int kv_heads, int dim, int vdim, int page_size, float scale) {
+                                                                   int rows, int heads, int kv_heads, int dim, int vdim, int page_size, float scale,
+                                                                   float* __restrict__ ws, int tiles_a_chunk, int max_chunks) {
   extern __shared__ __align__(16) unsigned char sm_raw[];
   const int ldq = dim + 8, ldv = vdim + 8;                    // padded rows: 16-byte aligned, ldmatrix without bank conflicts
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(sm_raw);      // [64][dim + 8]
@@ -332,6 +335,7 @@ __global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const __nv_b
   const int p0 = positions[t0];
   if (p0 < 0) return;                                          // a padding row
   const int p_last = p0 + n_valid - 1;
+  if ((int)blockIdx.z * tiles_a_chunk > p_last / kSmTile) return;      // the tile's keys end before this block's chunk
   const int32_t* pages = kv_indices + kv_indptr[r];
   const float slope = slopes[h], bias = head_bias[h];
   pdl_wait();
@@ -354,12 +358,18 @@ __global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const __nv_b
   const int row_lo = warp * 16 + (lane >> 2);                 // the thread's two query rows within the tile: row_lo and row_lo + 8
   const int pos_lo = p0 + row_lo, pos_hi = pos_lo + 8;
   const int vchunks = vdim / 8;
-  const int n_tiles = p_last / kSmTile + 1;
+  // the tile's keys in chunks of tiles_a_chunk key tiles, a chunk a block (blockIdx.z); with more than one chunk the blocks leave
+  // their sums in ws and a second kernel adds them in order
+  const int all_tiles = p_last / kSmTile + 1;
+  const int n_chunks = (all_tiles + tiles_a_chunk - 1) / tiles_a_chunk;
+  const int first_tile = (int)blockIdx.z * tiles_a_chunk;
+  if (first_tile >= all_tiles) return;
+  const int n_tiles = min(all_tiles, first_tile + tiles_a_chunk);
   // a tile's keys and values come by asynchronous 16-byte copies (a key after the block's last query: zeros), one tile ahead
   auto fetch = [&](int kt) {
     const int k0 = kt * kSmTile;
-    __nv_bfloat16* Kd = Kb + (kt & 1) * kSmTile * ldq;
-    __nv_bfloat16* Vd = Vb + (kt & 1) * kSmTile * ldv;
+    __nv_bfloat16* Kd = Kb + ((kt - first_tile) & 1) * kSmTile * ldq;
+    __nv_bfloat16* Vd = Vb + ((kt - first_tile) & 1) * kSmTile * ldv;
     for (int idx = tid; idx < kSmTile * (qchunks + vchunks); idx += 128) {
       const bool is_k = idx < kSmTile * qchunks;
       const int i2 = is_k ? idx : idx - kSmTile * qchunks;
@@ -374,11 +384,11 @@ __global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const __nv_b
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   };
-  fetch(0);
-  for (int kt = 0; kt < n_tiles; ++kt) {
+  fetch(first_tile);
+  for (int kt = first_tile; kt < n_tiles; ++kt) {
     const int k0 = kt * kSmTile;
-    const __nv_bfloat16* Ks = Kb + (kt & 1) * kSmTile * ldq;
-    const __nv_bfloat16* Vs = Vb + (kt & 1) * kSmTile * ldv;
+    const __nv_bfloat16* Ks = Kb + ((kt - first_tile) & 1) * kSmTile * ldq;
+    const __nv_bfloat16* Vs = Vb + ((kt - first_tile) & 1) * kSmTile * ldv;
     if (kt + 1 < n_tiles) {
       fetch(kt + 1);
       asm volatile("cp.async.wait_group 1;\n" ::: "memory");
@@ -445,6 +455,22 @@ __global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const __nv_b
     }
     __syncthreads();                                           // everybody is done with the buffer the next fetch fills
   }
+  if (n_chunks > 1) {                                          // the chunk's sums, for the kernel that adds a tile's chunks
+#pragma unroll
+    for (int n = 0; n < VMAX / 8; ++n) {
+      if (n * 8 < vdim) {
+        const int c = n * 8 + (lane & 3) * 2;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int row = row_lo + half * 8;
+          if (row < n_valid)
+            *reinterpret_cast<float2*>(ws + ((((size_t)(t0 + row) * heads + h) * max_chunks + blockIdx.z) * vdim + c)) =
+                make_float2(o[n][2 * half], o[n][2 * half + 1]);
+        }
+      }
+    }
+    return;
+  }
   // the output gate and the one rounding
 #pragma unroll
   for (int n = 0; n < VMAX / 8; ++n) {
@@ -468,6 +494,32 @@ __global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const __nv_b
   }
 }
 
+// A block a token: where the token's tile of queries had its keys in several chunks, their sums are added in chunk order, then the
+// output gate and the one rounding.
+__global__ void sigmoid_mma_merge_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate,
+                                         int64_t ld_gate, const int32_t* __restrict__ positions, const int32_t* __restrict__ token_row,
+                                         const int32_t* __restrict__ q_indptr, int heads, int vdim, int tiles_a_chunk, int max_chunks) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  if (positions[t] < 0) return;
+  const int r = token_row[t];
+  const int t0 = q_indptr[r] + (t - q_indptr[r]) / kSmTile * kSmTile;
+  const int n_valid = min(kSmTile, q_indptr[r + 1] - t0);
+  const int all_tiles = (positions[t0] + n_valid - 1) / kSmTile + 1;
+  const int n_chunks = (all_tiles + tiles_a_chunk - 1) / tiles_a_chunk;
+  if (n_chunks <= 1) return;                                   // the attention kernel wrote the token's output itself
+  const int width = heads * vdim;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const int h = i / vdim, c = i % vdim;
+    const float* src = ws + (((size_t)t * heads + h) * max_chunks) * vdim + c;
+    float a = 0.f;
+    for (int z = 0; z < n_chunks; ++z) a += src[(size_t)z * vdim];
+    if (gate != nullptr) a *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[(size_t)t * ld_gate + i])));
+    out[(size_t)t * width + i] = __float2bfloat16_rn(a);
+  }
+}
+
 }  // namespace roost
 
 extern "C" int roost_sigmoid_attention_mma_supported(int dim, int vdim, int entry) {
@@ -477,8 +529,9 @@ extern "C" int roost_sigmoid_attention_mma_supported(int dim, int vdim, int entr
 // q [tokens, heads, dim], out [tokens, heads * vdim], both bfloat16; rows: the step's rows (q_indptr has rows + 1 entries).
 extern "C" int roost_sigmoid_attention_mma(const void* q, void* out, const void* k_base, const void* v_base, int entry, const void* gate, int64_t ld_gate,
                                            const float* slopes, const float* head_bias, const int32_t* positions, const int32_t* q_indptr,
-                                           const int32_t* kv_indptr, const int32_t* kv_indices, int tokens, int rows, int heads, int kv_heads, int dim,
-                                           int vdim, int page_size, float scale, roost_stream_t stream) {
+                                           const int32_t* token_row, const int32_t* kv_indptr, const int32_t* kv_indices, int tokens, int rows, int heads,
+                                           int kv_heads, int dim, int vdim, int page_size, float scale, float* ws, int tiles_a_chunk, int max_chunks,
+                                           roost_stream_t stream) {
   ROOST_REQUIRE(tokens >= 0 && rows >= 0 && heads > 0 && kv_heads > 0 && page_size > 0 && heads % kv_heads == 0, "sigmoid_attention_mma: sizes must be positive");
   ROOST_REQUIRE(q && out && k_base && v_base && slopes && head_bias && positions && q_indptr && kv_indptr && kv_indices,
                 "sigmoid_attention_mma: a pointer is null");
@@ -486,22 +539,27 @@ extern "C" int roost_sigmoid_attention_mma(const void* q, void* out, const void*
   ROOST_REQUIRE((uintptr_t)q % 16 == 0 && (uintptr_t)k_base % 16 == 0 && (uintptr_t)v_base % 16 == 0 && (uintptr_t)out % 4 == 0 &&
                     (gate == nullptr || ((uintptr_t)gate % 4 == 0 && ld_gate % 2 == 0 && ld_gate >= (int64_t)heads * vdim)),
                 "sigmoid_attention_mma: a pointer is not aligned");
+  ROOST_REQUIRE(tiles_a_chunk >= 1 && max_chunks >= 1 && (max_chunks == 1 || (ws != nullptr && token_row != nullptr)),
+                "sigmoid_attention_mma: chunks of keys need a workspace for their sums");
   if (tokens == 0 || rows == 0) return ROOST_OK;
-  if (heads > 65535) return fail(ROOST_ERR_UNSUPPORTED, "sigmoid_attention_mma: too many heads");
+  if (heads > 65535 || max_chunks > 65535) return fail(ROOST_ERR_UNSUPPORTED, "sigmoid_attention_mma: too many heads or chunks");
   const size_t smem = ((size_t)3 * kSmTile * (dim + 8) + (size_t)2 * kSmTile * (vdim + 8)) * sizeof(__nv_bfloat16);
-  dim3 grid((tokens + kSmTile - 1) / kSmTile + rows, heads);
+  dim3 grid((tokens + kSmTile - 1) / kSmTile + rows, heads, max_chunks);
 #define ROOST_SG_MMA(DMAX, VMAX)                                                                                                                  \
   do {                                                                                                                                            \
     auto kernel = sigmoid_attention_mma_kernel<DMAX, VMAX>;                                                                                       \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                                   \
     launch_kernel(kernel, grid, dim3(128), smem, (cudaStream_t)stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_base, \
                   (const __nv_bfloat16*)v_base, entry, (const __nv_bfloat16*)gate, ld_gate, slopes, head_bias, positions, q_indptr, kv_indptr,    \
-                  kv_indices, rows, heads, kv_heads, dim, vdim, page_size, scale);                                                                \
+                  kv_indices, rows, heads, kv_heads, dim, vdim, page_size, scale, ws, tiles_a_chunk, max_chunks);                                 \
   } while (0)
   if (dim <= 64 && vdim <= 64) ROOST_SG_MMA(64, 64);
   else if (dim <= 64) ROOST_SG_MMA(64, 128);
   else if (vdim <= 64) ROOST_SG_MMA(128, 64);
   else ROOST_SG_MMA(128, 128);
 #undef ROOST_SG_MMA
+  if (max_chunks > 1)
+    launch_kernel(sigmoid_mma_merge_kernel, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, (const float*)ws, (__nv_bfloat16*)out,
+                  (const __nv_bfloat16*)gate, ld_gate, positions, token_row, q_indptr, heads, vdim, tiles_a_chunk, max_chunks);
   return check_launch("sigmoid_attention_mma");
 }

@@ -168,7 +168,7 @@ _SIGNATURES = {
                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
     "roost_sigmoid_attention_mma_supported": [c_int, c_int, c_int],
     "roost_sigmoid_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p],
     "roost_xielu": [c_void_p, c_void_p, c_int64, c_float, c_float, c_int, c_void_p],
     "roost_head_gate_mul": [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "roost_wide_rms_norm_gated": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
@@ -1118,6 +1118,7 @@ class KernelLibrary:
         return q
 
     SIGMOID_MMA_MIN_TOKENS = 32     # tokens from which a bfloat16 step that brings prompt portions runs the tensor-core form
+    SIGMOID_MMA_CHUNK_TILES = 8     # tiles of 64 keys a block of the tensor-core form takes of a long row
 
     def sigmoid_attention_mma_supported(self, dim: int, vdim: int, two_planes: bool) -> bool:
         return bool(self._lib.roost_sigmoid_attention_mma_supported(int(dim), int(vdim), int(dim if two_planes else dim + vdim)))
@@ -1144,9 +1145,16 @@ class KernelLibrary:
         out = torch.empty((T, heads * vdim), dtype=q.dtype, device=q.device)
         if q_indptr is not None and q.dtype == torch.bfloat16 and self.sigmoid_attention_mma_supported(dim, vdim, v_pool is not None):
             _need(q_indptr, "q_indptr", torch.int32)
+            # rows of more than SIGMOID_MMA_CHUNK_TILES tiles of 64 keys have the keys of their later queries dealt to several blocks;
+            # the bound on the requests' lengths says how many (every replay of a captured step agrees)
+            per = self.SIGMOID_MMA_CHUNK_TILES
+            chunks = -(-(kv_cap // 64 + 1) // per) if kv_cap else 1
+            if chunks == 1:
+                per = 1 << 24
+            ws = torch.empty((T * heads * chunks * vdim,), dtype=torch.float32, device=q.device) if chunks > 1 else None
             self._call("roost_sigmoid_attention_mma", _ptr(q), _ptr(out), kb, vb, entry, gate_ptr, ld_gate, _ptr(slopes), _ptr(head_bias), _ptr(positions),
-                       _ptr(q_indptr), _ptr(kv_indptr), _ptr(kv_indices), T, q_indptr.numel() - 1, heads, kv_heads, dim, vdim, k_pool.shape[2],
-                       float(scale), _stream())
+                       _ptr(q_indptr), _ptr(token_row), _ptr(kv_indptr), _ptr(kv_indices), T, q_indptr.numel() - 1, heads, kv_heads, dim, vdim,
+                       k_pool.shape[2], float(scale), _ptr(ws), per, chunks, _stream(), launches=2 if chunks > 1 else 1)
             return out
         gy = kv_heads * (-(-(heads // kv_heads) // 8))
         splits, per = self.sink_splits_for(T, gy, kv_cap) if kv_cap else (1, 1 << 24)

@@ -154,8 +154,19 @@ def test_the_attention_with_sigmoid_weights(kernels, dtype, heads, kv_heads, dim
         q_indptr = i32([0, lens[0], T])
         for rows, col in ((dev, width), (None, None)):
             got = kernels.sigmoid_attention(q, k_pool, v_pool, rows, col, slopes.cuda(), bias.cuda(), positions.cuda(), token_row.cuda(), kv_indptr,
-                                            kv_indices, kv_heads, vdim, scale, kv_cap=128, q_indptr=q_indptr)
+                                            kv_indices, kv_heads, vdim, scale, kv_cap=160, q_indptr=q_indptr)
             close(got.cpu(), gated if rows is not None else want.reshape(T, -1), dtype, "sigmoid attention on the tensor cores")
+        # a long row's keys dealt to several blocks in chunks of one and of two tiles of 64 keys (the kernel's own chunk is longer than
+        # these rows): the second row's later queries have two and three chunks, the first row's one
+        kept = kernels.SIGMOID_MMA_CHUNK_TILES
+        try:
+            for tiles in (1, 2):
+                kernels.SIGMOID_MMA_CHUNK_TILES = tiles
+                got = kernels.sigmoid_attention(q, k_pool, v_pool, dev, width, slopes.cuda(), bias.cuda(), positions.cuda(), token_row.cuda(), kv_indptr,
+                                                kv_indices, kv_heads, vdim, scale, kv_cap=1024, q_indptr=q_indptr)
+                close(got.cpu(), gated, dtype, f"sigmoid attention on the tensor cores, chunks of {tiles} tiles")
+        finally:
+            kernels.SIGMOID_MMA_CHUNK_TILES = kept
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
