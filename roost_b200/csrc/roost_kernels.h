@@ -475,7 +475,7 @@ int roost_sigmoid_attention_mma(const void* q, void* out, const void* k_base, co
                                 const int32_t* token_row, const int32_t* kv_indptr, const int32_t* kv_indices, int tokens, int rows, int heads,
                                 int kv_heads, int dim, int vdim, int page_size, float scale, float* ws, int tiles_a_chunk, int max_chunks,
                                 roost_stream_t stream);   /* max_chunks > 1: a tile's keys in chunks of tiles_a_chunk tiles of 64 keys, their sums
-                                                             in ws: float[tokens * heads * max_chunks * vdim]; max_chunks must cover the longest row */
+                                                             in ws: float[tokens * heads * max_chunks * vdim]; the last chunk takes what a longer row has left */
 
 /* ---- activations.cu ---- */
 /* y = a_pos z^2 + z / 2 (z > 0), a_neg (exp(z) - 1 - z) + z / 2 (z <= 0). */

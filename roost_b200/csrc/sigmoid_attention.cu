@@ -111,7 +111,8 @@ __global__ void __launch_bounds__(kSgWarps * 32) sigmoid_attention_kernel(const 
 #pragma unroll
   for (int c = 0; c < kSgMaxDim / 32; ++c) acc[c] = 0.f;
   const int n_tiles = pos / kSgTile + 1;
-  const int first = z * tiles_per_split, last = min(n_tiles, first + tiles_per_split);
+  // the last split takes whatever is left: a bound on the lengths that a row exceeds costs balance, not keys
+  const int first = z * tiles_per_split, last = z == splits - 1 ? n_tiles : min(n_tiles, first + tiles_per_split);
   for (int tile = first; tile < last; ++tile) {
     const int k0 = tile * kSgTile;
     __syncthreads();
@@ -361,10 +362,11 @@ __global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const __nv_b
   // the tile's keys in chunks of tiles_a_chunk key tiles, a chunk a block (blockIdx.z); with more than one chunk the blocks leave
   // their sums in ws and a second kernel adds them in order
   const int all_tiles = p_last / kSmTile + 1;
-  const int n_chunks = (all_tiles + tiles_a_chunk - 1) / tiles_a_chunk;
+  const int n_chunks = min((all_tiles + tiles_a_chunk - 1) / tiles_a_chunk, max_chunks);
   const int first_tile = (int)blockIdx.z * tiles_a_chunk;
   if (first_tile >= all_tiles) return;
-  const int n_tiles = min(all_tiles, first_tile + tiles_a_chunk);
+  // the launch's last chunk takes whatever is left: a bound on the lengths that a row exceeds costs balance, not keys
+  const int n_tiles = (int)blockIdx.z == max_chunks - 1 ? all_tiles : min(all_tiles, first_tile + tiles_a_chunk);
   // a tile's keys and values come by asynchronous 16-byte copies (a key after the block's last query: zeros), one tile ahead
   auto fetch = [&](int kt) {
     const int k0 = kt * kSmTile;
@@ -507,7 +509,7 @@ __global__ void sigmoid_mma_merge_kernel(const float* __restrict__ ws, __nv_bflo
   const int t0 = q_indptr[r] + (t - q_indptr[r]) / kSmTile * kSmTile;
   const int n_valid = min(kSmTile, q_indptr[r + 1] - t0);
   const int all_tiles = (positions[t0] + n_valid - 1) / kSmTile + 1;
-  const int n_chunks = (all_tiles + tiles_a_chunk - 1) / tiles_a_chunk;
+  const int n_chunks = min((all_tiles + tiles_a_chunk - 1) / tiles_a_chunk, max_chunks);
   if (n_chunks <= 1) return;                                   // the attention kernel wrote the token's output itself
   const int width = heads * vdim;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {

@@ -145,7 +145,7 @@ def test_the_attention_with_sigmoid_weights(kernels, dtype, heads, kv_heads, dim
     close(got.cpu(), want.reshape(T, -1), dtype, "sigmoid attention without a gate")
     # a step of few tokens deals every token's keys to several blocks: the last tokens of both rows and two in between
     few = torch.tensor([31, 44, 45, 45 + 63, 45 + 64, T - 1])
-    for kv_cap in (160, 1024):
+    for kv_cap in (160, 1024, 96):       # the last: a bound the second row exceeds
         got = kernels.sigmoid_attention(q[few.cuda()].contiguous(), k_pool, v_pool, dev[few.cuda()].contiguous(), width, slopes.cuda(), bias.cuda(),
                                         positions[few].cuda(), token_row[few].cuda(), kv_indptr, kv_indices, kv_heads, vdim, scale, kv_cap=kv_cap)
         close(got.cpu(), gated[few], dtype, f"sigmoid attention of few tokens, bound {kv_cap}")
@@ -160,11 +160,11 @@ def test_the_attention_with_sigmoid_weights(kernels, dtype, heads, kv_heads, dim
         # these rows): the second row's later queries have two and three chunks, the first row's one
         kept = kernels.SIGMOID_MMA_CHUNK_TILES
         try:
-            for tiles in (1, 2):
+            for tiles, kv_cap in ((1, 1024), (2, 1024), (1, 64)):      # the last: a bound the second row exceeds (two chunks for three tiles)
                 kernels.SIGMOID_MMA_CHUNK_TILES = tiles
                 got = kernels.sigmoid_attention(q, k_pool, v_pool, dev, width, slopes.cuda(), bias.cuda(), positions.cuda(), token_row.cuda(), kv_indptr,
-                                                kv_indices, kv_heads, vdim, scale, kv_cap=1024, q_indptr=q_indptr)
-                close(got.cpu(), gated, dtype, f"sigmoid attention on the tensor cores, chunks of {tiles} tiles")
+                                                kv_indices, kv_heads, vdim, scale, kv_cap=kv_cap, q_indptr=q_indptr)
+                close(got.cpu(), gated, dtype, f"sigmoid attention on the tensor cores, chunks of {tiles} tiles under a bound of {kv_cap}")
         finally:
             kernels.SIGMOID_MMA_CHUNK_TILES = kept
 
