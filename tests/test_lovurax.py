@@ -354,13 +354,13 @@ def filler(cfg, n, seed):
 @pytest.mark.parametrize("decoded", [False, True], ids=["in a prompt", "decoded"])
 @pytest.mark.parametrize("kind", sorted(FAR))
 def test_a_key_far_away_among_hundreds_at_every_page_offset(tmp_path_factory, backend, kind, decoded):
-    """The key token sits 288 to 321 places before the query token, once at every offset of a page of four and across the
-    borders of the 32-key tiles; losing that one key (a wrong page, a tile's or a split's edge, a state cut short) changes the
+    """The key token sits 256 to 321 places before the query token, once at every offset of a page of four and across the
+    borders of the 32- and 64-key tiles; losing that one key (a wrong page, a tile's or a split's edge, a state cut short) changes the
     query's logits by far more than the bound, which the test checks on the plain logits with and without the key."""
     folder, cfg, weights = sharpened(tmp_path_factory, kind)
     run = Run(folder, cfg, backend, page_size=4, num_pages=120)
     seen = {}
-    for at in (None, 0, 1, 2, 3, 31, 32, 33):
+    for at in (None, 0, 1, 2, 3, 31, 32, 33, 63, 64, 65):
         ids = filler(cfg, 330, seed=4)
         if at is not None:
             ids[at] = KEY
@@ -376,7 +376,7 @@ def test_a_key_far_away_among_hundreds_at_every_page_offset(tmp_path_factory, ba
         run.finish(rid)
         got, want = run.check(rid, ids, weights, f"{kind}: far key at {at}")
         seen[at] = (got[321], want[321])
-    for at in (0, 1, 2, 3, 31, 32, 33):
+    for at in (0, 1, 2, 3, 31, 32, 33, 63, 64, 65):
         moved = H.rms_error(seen[at][1][None], seen[None][1][None])
         off = H.rms_error(seen[at][0][None], seen[at][1][None])
         print(f"MEASURED {kind}: the key at {at} moves the query's logits by {moved:.3f}; the engine is {off:.2e} from the plain logits with it")
