@@ -477,6 +477,17 @@ int roost_sigmoid_attention_mma(const void* q, void* out, const void* k_base, co
                                 roost_stream_t stream);   /* max_chunks > 1: a tile's keys in chunks of tiles_a_chunk tiles of 64 keys, their sums
                                                              in ws: float[tokens * heads * max_chunks * vdim]; the last chunk takes what a longer row has left */
 
+/* ---- carried_attention.cu: prompt portions over keys and values carried out of a latent cache for the step (bfloat16) ---- */
+/* out [rows * stride, width]: entry r * stride + j is the cached vector of row r's token at position j, zeros from kv_lens[r] on. */
+int roost_latent_gather(const void* pool, void* out, const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, int rows,
+                        int stride, int width, int page_size, roost_stream_t stream);
+int roost_carried_attention_supported(int dim, int vdim);   /* multiples of 16 up to 128 */
+/* Causal softmax attention of the step's queries (rows ld_q apart, head h at column h * dim) over keys [rows * stride, heads * dim] and
+ * values [rows * stride, heads * vdim] laid out like the gather's output: out [tokens, heads * vdim]. */
+int roost_carried_attention(const void* q, int64_t ld_q, void* out, const void* keys, const void* values, const int32_t* positions,
+                            const int32_t* q_indptr, int tokens, int rows, int heads, int dim, int vdim, int stride, float scale,
+                            roost_stream_t stream);
+
 /* ---- activations.cu ---- */
 /* y = a_pos z^2 + z / 2 (z > 0), a_neg (exp(z) - 1 - z) + z / 2 (z <= 0). */
 int roost_xielu(const void* x, void* out, int64_t n, float a_pos, float a_neg, int dtype, roost_stream_t stream);

@@ -169,6 +169,10 @@ _SIGNATURES = {
     "roost_sigmoid_attention_mma_supported": [c_int, c_int, c_int],
     "roost_sigmoid_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p],
+    "roost_latent_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "roost_carried_attention_supported": [c_int, c_int],
+    "roost_carried_attention": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                c_void_p],
     "roost_xielu": [c_void_p, c_void_p, c_int64, c_float, c_float, c_int, c_void_p],
     "roost_head_gate_mul": [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "roost_wide_rms_norm_gated": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
@@ -665,6 +669,35 @@ class KernelLibrary:
         self._call("roost_latent_attention", _ptr(q_latent), _ptr(q), _ptr(out), _ptr(part), _ptr(pool), _ptr(positions), _ptr(token_row),
                    _ptr(kv_indptr), _ptr(kv_indices), T, heads, nope, rope, rank, pool.shape[2], scale, int(window) if window else 0, splits,
                    dtype_code(q.dtype), _stream(), launches=2 if splits > 1 else 1)
+        return out
+
+    # ------------------------------------------------------------------ prompt portions over keys and values carried out of a latent cache
+    def latent_gather(self, pool, kv_lens, kv_indptr, kv_indices, rows: int, stride: int) -> torch.Tensor:
+        """[rows * stride, width]: entry r * stride + j is the cached vector of row r's token at position j (zeros beyond the row)."""
+        _need(pool, "pool", torch.bfloat16)
+        for n, t in (("kv_lens", kv_lens), ("kv_indptr", kv_indptr), ("kv_indices", kv_indices)):
+            _need(t, n, torch.int32)
+        if pool.shape[1] != 1 or kv_lens.numel() < rows:
+            raise KernelError("latent_gather: a pool of one vector a token and a length a row")
+        out = torch.empty((rows * stride, pool.shape[3]), dtype=pool.dtype, device=pool.device)
+        self._call("roost_latent_gather", _ptr(pool), _ptr(out), _ptr(kv_lens), _ptr(kv_indptr), _ptr(kv_indices), rows, stride, pool.shape[3],
+                   pool.shape[2], _stream())
+        return out
+
+    def carried_attention_supported(self, dim: int, vdim: int) -> bool:
+        return bool(self._lib.roost_carried_attention_supported(int(dim), int(vdim)))
+
+    def carried_attention(self, q, keys, values, positions, q_indptr, heads: int, dim: int, vdim: int, stride: int, scale: float) -> torch.Tensor:
+        """Causal softmax attention of the step's queries q [T, >= heads * dim] over keys [rows * stride, heads * dim] and values
+        [rows * stride, heads * vdim] (entry r * stride + j: row r's token at position j): [T, heads * vdim], bfloat16 on the tensor cores."""
+        _need(q, "q", torch.bfloat16); _need(keys, "keys", torch.bfloat16); _need(values, "values", torch.bfloat16)
+        _need(positions, "positions", torch.int32); _need(q_indptr, "q_indptr", torch.int32)
+        T, rows = q.shape[0], q_indptr.numel() - 1
+        if q.shape[1] < heads * dim or tuple(keys.shape) != (rows * stride, heads * dim) or tuple(values.shape) != (rows * stride, heads * vdim):
+            raise KernelError("carried_attention: the queries, keys or values do not fit the sizes")
+        out = torch.empty((T, heads * vdim), dtype=q.dtype, device=q.device)
+        self._call("roost_carried_attention", _ptr(q), q.stride(0), _ptr(out), _ptr(keys), _ptr(values), _ptr(positions), _ptr(q_indptr), T, rows, heads,
+                   dim, vdim, stride, float(scale), _stream())
         return out
 
     # ------------------------------------------------------------------ the Mamba-2 recurrence

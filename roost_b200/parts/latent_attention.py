@@ -14,7 +14,9 @@ cache entry; the batched product into the latent space; attention; the batched p
 projection. A run that reads another run's cache makes no latent and writes nothing; its window may differ from the
 owner's (the cache is kept for the widest). With ``rope_dim`` 0 keys and queries have no rotated part: nothing is rotated and the
 cache entry is the latent alone. With ``head_gate`` one more small projection gives a number a token and head, and a kernel
-multiplies every head's output by its sigmoid before the output projection.
+multiplies every head's output by its sigmoid before the output projection. bfloat16 steps of prompt portions of such a run (no
+rotated part, no window) carry the rows' cached latents out to keys and values a head (a gather and two products) and attend there
+on the tensor cores: a prompt needs a quarter of the products that way when the latent is four times as wide as a head.
 """
 from __future__ import annotations
 
@@ -51,6 +53,16 @@ class LatentAttention(Mixer):
         self.out = Linear(runtime, s.hidden, s.num_heads * s.v_dim)
         self.position = POSITIONS.build(s.position, runtime) if s.rope_dim else None
         self.head_gate = Linear(runtime, s.num_heads, s.hidden) if s.head_gate else None
+        # Prompt portions of a run without a rotated part and without a window may leave the latent space: the rows' cached latents
+        # are carried out to keys and values a head by two products, and the attention runs over those, a quarter of the products
+        # the latent space costs when the latent is four times as wide as a head. Decode steps stay in the latent space, where the
+        # cache is read once for all heads.
+        self.carried = (s.rope_dim == 0 and s.window is None and s.own_latent and not runtime.full_precision and runtime.kernels is not None
+                        and getattr(runtime.kernels, "carried_attention_supported", lambda d, v: False)(s.nope_dim, s.v_dim))
+        self.key_full = Linear(runtime, s.num_heads * s.nope_dim, s.kv_rank) if self.carried else None
+        self.value_full = Linear(runtime, s.num_heads * s.v_dim, s.kv_rank) if self.carried else None
+        self.carried_min_tokens = 128        # tokens of a step from which its prompt portions are worth the two products
+        self.carried_max_entries = 16384     # rows x the bound on their lengths up to which the carried keys and values are made
         self.key_up: torch.Tensor | None = None      # [heads, kv_rank, nope_dim]: W_uk,h^T as a weight stored [out, in]
         self.value_up: torch.Tensor | None = None    # [heads, v_dim, kv_rank]
         self.latent_weight: torch.Tensor | None = None
@@ -76,6 +88,9 @@ class LatentAttention(Mixer):
         self.value_up = params["uv"].to(self.rt.dtype).reshape(s.num_heads, s.v_dim, s.kv_rank).contiguous()
         if s.head_gate:
             self.head_gate.load(params["head_gate"])
+        if self.carried:
+            self.key_full.load(params["uk"])
+            self.value_full.load(params["uv"])
         if s.own_latent:
             self.down.load(params["dkv"])
             self.latent_weight = params["latent_norm"].float().contiguous()
@@ -95,6 +110,15 @@ class LatentAttention(Mixer):
         down = self.down(x) if s.own_latent else None                       # [T, kv_rank + rope]
         k.latent_prepare(q, down, cache.k_pool, self.latent_weight, inv_freq, rotary_dim, batch.positions,
                          tables.slot_mapping if s.own_latent else None, H, s.nope_dim, s.rope_dim, s.kv_rank, s.latent_eps, cache.page_size)
+        if (self.carried and not batch.all_single and T >= self.carried_min_tokens and batch.kv_cap
+                and batch.num_rows * batch.kv_cap <= self.carried_max_entries):
+            # a function of the step's sizes and kind only, so a captured step keeps its way
+            latents = k.latent_gather(cache.k_pool, batch.kv_lens, tables.kv_indptr, tables.kv_indices, batch.num_rows, batch.kv_cap)
+            o = k.carried_attention(q, self.key_full(latents), self.value_full(latents), batch.positions, batch.q_indptr, H, s.nope_dim, s.v_dim,
+                                    batch.kv_cap, s.scale)
+            if s.head_gate:
+                k.head_gate_mul_(o, self.head_gate(x), 0, H)
+            return self.out(o)
         q_heads = q.view(T, H, self.q_head).transpose(0, 1)                 # [H, T, nope + rope], a view
         q_latent = torch.empty((H, T, s.kv_rank), dtype=q.dtype, device=q.device)
         batched_linear(self.rt, q_heads[:, :, : s.nope_dim], self.key_up, q_latent)

@@ -293,12 +293,13 @@ def test_long_decoding_over_many_pages(model, backend):
 
 LONG = LM.config([(LM.retention(heads=2, dim=20, vdim=36, decay=(0.98, 0.999), rot=8, base=10000.0), LM.dense(ff=128)),
                   (LM.attention(heads=4, kv_heads=2, dim=16, vdim=24, scale=0.25, coef=0.2, every=100), None),
-                  (LM.latent(heads=2, dim=16, vdim=12, rank=32, scale=0.25), LM.dense(ff=96))], width=72, vocab=83, logit_scale=1.25)
+                  (LM.latent(heads=2, dim=16, vdim=32, rank=40, scale=0.25), LM.dense(ff=96))], width=72, vocab=83, logit_scale=1.25)
 
 
 def test_a_long_prompt_takes_the_forms_of_steps_of_many_rows(tmp_path_factory, backend):
     """700 tokens in one step and then 2 + 1: the kernels' forms for many tokens a row (the retention cut into chunks of 64
-    tokens whose states are carried from chunk to chunk, the last chunk a partial one)."""
+    tokens whose states are carried from chunk to chunk, the last chunk a partial one; the attention on the tensor cores; the latent
+    attention over keys and values carried out of the cache)."""
     folder, cfg, weights = model_dir(tmp_path_factory, "long", LONG, seed=21)
     run = Run(folder, cfg, backend, page_size=16, num_pages=64)
     ids = ids_for(cfg, 703, seed=8)

@@ -209,3 +209,41 @@ def test_the_gated_sum_into_the_stream_and_its_norm(kernels, dtype, hidden):
     got = kernels.wide_rms_norm_gated(dev, w.cuda(), eps, dtype, y.cuda(), arguments.cuda(), bias.cuda())
     close(got.cpu(), P.rms_norm(total, w.double(), eps), dtype, "gated sum and norm")
     close(dev.cpu(), total, torch.float32, "the stream after the sum", f32=1e-6)
+
+
+@pytest.mark.parametrize("heads,dim,vdim,width", [(3, 16, 48, 24), (2, 64, 64, 256), (1, 128, 32, 40), (4, 32, 128, 64)])
+def test_prompt_portions_over_keys_and_values_carried_out_of_a_latent_cache(kernels, heads, dim, vdim, width):
+    """The gather of two rows' cached vectors from scattered pages into dense stretches (zeros beyond a row), and the causal softmax
+    attention over keys and values laid out that way: rows of 45 and 150 tokens whose queries are the second row's last 100 tokens and
+    all of the first row's, so that a row's queries start inside its keys."""
+    g = torch.Generator().manual_seed(heads * dim + vdim)
+    page, stride, scale = 4, 192, 1.3 / math.sqrt(dim)
+    lens = [45, 150]
+    pages_of = [torch.randperm(40, generator=g)[:12].tolist(), (40 + torch.randperm(40, generator=g)[:38]).tolist()]
+    pool = torch.randn(80, 1, page, width, generator=g).to(torch.bfloat16).cuda()
+    kv_indptr, kv_indices = i32([0, 12, 50]), i32(pages_of[0] + pages_of[1])
+    latents = kernels.latent_gather(pool, i32(lens), kv_indptr, kv_indices, 2, stride)
+    want = torch.zeros(2 * stride, width, dtype=torch.bfloat16)
+    for r, n in enumerate(lens):
+        for j in range(n):
+            want[r * stride + j] = pool[pages_of[r][j // page], 0, j % page].cpu()
+    assert torch.equal(latents.cpu(), want)
+    keys = torch.randn(2 * stride, heads * dim, generator=g).to(torch.bfloat16)
+    values = torch.randn(2 * stride, heads * vdim, generator=g).to(torch.bfloat16)
+    starts = [0, 50]                                   # the first position each row brings queries for
+    positions = torch.cat([torch.arange(s0, n) for s0, n in zip(starts, lens)]).to(torch.int32)
+    T = positions.numel()
+    q = torch.randn(T, heads * dim + 8, generator=g).to(torch.bfloat16)         # other columns follow a token's queries
+    q_indptr = i32([0, lens[0] - starts[0], T])
+    got = kernels.carried_attention(q.cuda(), keys.cuda(), values.cuda(), positions.cuda(), q_indptr, heads, dim, vdim, stride, scale)
+    ref = torch.zeros(T, heads, vdim, dtype=torch.float64)
+    t = 0
+    for r, (s0, n) in enumerate(zip(starts, lens)):
+        K = keys[r * stride : r * stride + n].double().reshape(n, heads, dim)
+        V = values[r * stride : r * stride + n].double().reshape(n, heads, vdim)
+        for p in range(s0, n):
+            for h in range(heads):
+                w = torch.softmax((K[: p + 1, h] @ q[t, h * dim : (h + 1) * dim].double()) * scale, dim=0)
+                ref[t, h] = w @ V[: p + 1, h]
+            t += 1
+    close(got.cpu(), ref.reshape(T, -1), torch.bfloat16, "attention over carried keys and values")
